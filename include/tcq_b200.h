@@ -1,0 +1,139 @@
+/*
+ * C ABI of the B200 trellis codec (tail-biting bitshift-trellis Viterbi encoder
+ * and decoder, L = 16-bit state, T = 256 weights per tile, K = 2, 3 or 4 bits per
+ * weight, computed codebooks).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless its name ends
+ *     in _host.  The library never allocates or frees device memory; scratch is
+ *     passed in as `ws` (size from tcq_workspace_bytes()).
+ *   - `stream` is a cudaStream_t passed as void*.  All work is queued on it and
+ *     the call returns without synchronising.  Calls on different streams may
+ *     overlap if they use different workspaces.
+ *   - Return value: TCQ_OK (0) or a negative TCQ_E_* code; tcq_strerror() gives
+ *     the text.  Nothing is launched when an argument is rejected.
+ *   - Tiles are rows of 256 consecutive fp32 values; tile i starts at w + 256*i.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns TCQ_E_CUDA.
+ *
+ * Each entry point names the reference interface (file:line inside
+ * Azimml/trellis-everywhere) that it replaces.
+ */
+#ifndef TCQ_B200_H
+#define TCQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TCQ_API __attribute__((visibility("default")))
+#else
+#define TCQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCQ_T 256      /* weights per tile (src/trellis/qtip.py:23 T_SEQ) */
+#define TCQ_L 16       /* trellis state bits (src/trellis/qtip.py:21 L) */
+
+/* Codebook ids: the keys of CODEBOOKS, src/trellis/qtip.py:56. */
+#define TCQ_CB_1MAD 0  /* src/trellis/qtip.py:32-37 cb_1mad  */
+#define TCQ_CB_3INST 1 /* src/trellis/qtip.py:40-45 cb_3inst */
+#define TCQ_CB_MCG 2   /* src/trellis/qtip.py:48-53 cb_mcg   */
+
+#define TCQ_OK 0
+#define TCQ_E_BAD_K (-1)         /* K not in {2,3,4} */
+#define TCQ_E_BAD_CODEBOOK (-2)  /* codebook id unknown */
+#define TCQ_E_BAD_COUNT (-3)     /* negative tile / element count */
+#define TCQ_E_NULL_POINTER (-4)  /* a required pointer is NULL */
+#define TCQ_E_MISALIGNED (-5)    /* pointer not aligned as documented */
+#define TCQ_E_WORKSPACE (-6)     /* workspace smaller than tcq_workspace_min_bytes() */
+#define TCQ_E_CUDA (-7)          /* CUDA runtime error (no device, launch failure) */
+#define TCQ_E_BAD_ARGUMENT (-8)  /* other invalid argument (roll, T, ...) */
+
+/* Version of this ABI (bumped on any signature change). */
+TCQ_API int tcq_abi_version(void);
+
+/* Text for a return code.  Never NULL. */
+TCQ_API const char *tcq_strerror(int code);
+
+/* Text of the last CUDA error seen by this library on the calling thread. */
+TCQ_API const char *tcq_last_cuda_error(void);
+
+/*
+ * Scratch sizing.  tcq_workspace_bytes(): the size with which tcq_encode_tb /
+ * tcq_viterbi_pass process n_tiles at full speed (backpointers of up to one
+ * chunk of tiles, K bits per trellis edge per step, plus per-tile hand-off
+ * words).  tcq_workspace_min_bytes(): the smallest accepted size (one tile per
+ * SM-resident group); anything in between just means smaller chunks.
+ * Replaces the per-batch torch.empty scratch of
+ * src/trellis/viterbi_triton.py:96-102.  Returns 0 for invalid K.
+ */
+TCQ_API size_t tcq_workspace_bytes(int64_t n_tiles, int K);
+TCQ_API size_t tcq_workspace_min_bytes(int K);
+
+/*
+ * Tail-biting encode of n_tiles tiles.
+ * Replaces viterbi_tb (src/trellis/qtip.py:124-144) and viterbi_tb_triton
+ * (src/trellis/viterbi_triton.py:121-129), with pack_bits_np
+ * (scripts/export_packed_8b.py:52-62) fused into the traceback.
+ *   w       [n_tiles,256] fp32, 16-byte aligned, never written
+ *   packed  [n_tiles, 8*K] u32: bit kb of symbol t at bit (255-t)*K+kb   (required)
+ *   bits    [n_tiles,256] int64 symbols (< 2^K), or NULL
+ *   dq      [n_tiles,256] fp32 reconstruction codebook[state_t], or NULL
+ *   sse     [n_tiles] fp32 sum_t (w_t-dq_t)^2 accumulated in time order, or NULL
+ *   ws      scratch, 256-byte aligned, ws_bytes >= tcq_workspace_min_bytes(K)
+ */
+TCQ_API int tcq_encode_tb(const float *w, int64_t n_tiles, int K, int codebook, uint32_t *packed, int64_t *bits,
+                  float *dq, float *sse, void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * One Viterbi pass: the optimal state path of each tile.
+ * Replaces _viterbi_pass (src/trellis/qtip.py:147-196) and viterbi_pass_triton
+ * (src/trellis/viterbi_triton.py:81-118).
+ *   overlap [n_tiles] int32 edge (< 2^(16-K)) that the path must start from and
+ *           end at, or NULL for the unconstrained pass
+ *   roll    0, or 128 to run on the tile rotated by half its length
+ *           (torch.roll(w, 128, dims=1), src/trellis/qtip.py:138) without a copy
+ *   states  [n_tiles,256] int64 out
+ */
+TCQ_API int tcq_viterbi_pass(const float *w, int64_t n_tiles, int K, int codebook, const int32_t *overlap, int roll,
+                     int64_t *states, void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Decode packed tiles: dq[i,t] = codebook(16-bit window at bit (255-t)*K of tile
+ * i's words, wrapping past the last word).  Replaces lut[states2]
+ * (src/trellis/qtip.py:144), the wrapped-stream decode of tests/test_qtip.py:55-67
+ * and the WGSL window decode wz() (web/kernels.js:115-122).
+ *   packed [n_tiles, 8*K] u32, 4-byte aligned;  dq [n_tiles,256] fp32, 16-byte aligned
+ */
+TCQ_API int tcq_decode_packed(const uint32_t *packed, int64_t n_tiles, int K, int codebook, float *dq, void *stream);
+
+/*
+ * Decode unpacked symbol streams of any length T (no wrap): state_t is the last
+ * 16 bits of s0 followed by symbols 0..t.  Replaces decode_recursive and
+ * decode_window (src/trellis/qtip.py:70-110), which are equal by construction.
+ *   bits [n,T] int64;  s0 [n] int64 start states or NULL (zeros);  out [n,T] fp32
+ */
+TCQ_API int tcq_decode_symbols(const int64_t *bits, int64_t n, int64_t T, int K, int codebook, const int64_t *s0,
+                       float *out, void *stream);
+
+/*
+ * Pack symbols into the exporter's word layout.  Replaces pack_bits_np
+ * (scripts/export_packed_8b.py:52-62) for callers that already hold symbols.
+ *   bits [n_tiles,256] int64;  packed [n_tiles,8*K] u32
+ */
+TCQ_API int tcq_pack_symbols(const int64_t *bits, int64_t n_tiles, int K, uint32_t *packed, void *stream);
+
+/*
+ * Evaluate a computed codebook on all 65536 states.  Replaces codebook_lut
+ * (src/trellis/qtip.py:59-66).   lut [65536] fp32
+ */
+TCQ_API int tcq_codebook_lut(int codebook, float *lut, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCQ_B200_H */

@@ -1,0 +1,233 @@
+"""Parity of the CUDA codec (through the C ABI) with the CPU oracle and the reference's golden vectors.
+
+The bar is bit-exact for symbols, states, packed words and reconstructions; the per-tile
+squared error is the path metric accumulated in time order and is bit-exact as well.
+"""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import CODEBOOKS, KS, same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def q():
+    from trellis_b200 import qtip
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    qtip._lib.lib()                      # fails loudly if the extension is not built
+    return qtip
+
+
+def _np(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_codebook_tables(q, golden, luts, name):
+    lut = _np(q.codebook_lut(name, "cuda"))
+    assert same_bits(lut, luts[name])                                   # all 65536 states vs the oracle
+    sha = np.frombuffer(hashlib.sha256(lut.tobytes()).digest(), dtype=np.uint8)
+    assert np.array_equal(sha, golden["codebooks"][f"{name}_sha256"])   # and vs the reference's table
+
+
+def test_codebook_identification(q):
+    for name in CODEBOOKS:
+        assert q.codebook_id(q.codebook_lut(name, "cuda")) == q.CODEBOOK_IDS[name]
+        assert q.codebook_id(q.codebook_lut(name, "cpu")) == q.CODEBOOK_IDS[name]
+    with pytest.raises(ValueError):
+        q.codebook_id(torch.zeros(65536))
+    with pytest.raises(ValueError):
+        q.codebook_id("nope")
+
+
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_passes_match_reference(q, golden, name, K):
+    g = golden["encode"]
+    w = torch.from_numpy(g["w"]).cuda()
+    key = f"{name}_K{K}"
+    s1 = q.viterbi_pass_b200(w, K, None, name, roll=128)
+    assert np.array_equal(_np(s1), g[key + "_states1"].astype(np.int64))
+    s1b = q.viterbi_pass_b200(torch.roll(w, 128, dims=1), K, None, name)          # explicit roll, same thing
+    assert torch.equal(s1, s1b)
+    ov = torch.from_numpy(g[key + "_overlap"]).cuda()
+    s2 = q.viterbi_pass_b200(w, K, ov, name)
+    assert np.array_equal(_np(s2), g[key + "_states2"].astype(np.int64))
+
+
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_encode_matches_reference(q, oracle, golden, luts, name, K):
+    g = golden["encode"]
+    w = torch.from_numpy(g["w"]).cuda()
+    key = f"{name}_K{K}"
+    r = q.encode(w, K, name, want_bits=True)
+    assert np.array_equal(_np(r.bits), g[key + "_bits"].astype(np.int64))
+    assert same_bits(_np(r.dq), g[key + "_dq"])
+    assert np.array_equal(_np(r.packed).view(np.uint32), oracle.pack_bits(g[key + "_bits"], K))
+    _, _, sse = oracle.viterbi_tb(g["w"], K, luts[name], with_sse=True)
+    assert same_bits(_np(r.sse), sse)
+    bits, dq = q.viterbi_tb_b200(w, K, q.codebook_lut(name, "cuda"))             # the reference's call shape
+    assert torch.equal(bits, r.bits) and torch.equal(dq, r.dq)
+
+
+def test_encode_incoherence_processed_tiles(q, golden):
+    g = golden["encode_ip"]
+    r = q.encode(torch.from_numpy(g["w"]).cuda(), 3, "3inst", want_bits=True)
+    assert np.array_equal(_np(r.bits), g["bits"].astype(np.int64))
+    assert same_bits(_np(r.dq), g["dq"])
+
+
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_encode_matches_oracle_on_fresh_tiles(q, oracle, luts, name, K):
+    # 37 tiles: not a multiple of any tile-group size, so the ragged last group is exercised
+    rng = np.random.default_rng(1000 + 10 * K + CODEBOOKS.index(name))
+    w = (rng.standard_normal((37, 256)) * 1.2437).astype(np.float32)
+    w[3] = 0.0                                   # constant tile: every path ties somewhere
+    w[5] *= 30.0                                 # far outside the codebook's range
+    w[7, ::2] = luts[name][rng.integers(0, 65536, 128)]   # exact codebook values
+    bits, dq, sse = oracle.viterbi_tb(w, K, luts[name], with_sse=True)
+    r = q.encode(torch.from_numpy(w).cuda(), K, name, want_bits=True)
+    assert np.array_equal(_np(r.bits), bits)
+    assert same_bits(_np(r.dq), dq)
+    assert same_bits(_np(r.sse), sse)
+    assert np.array_equal(_np(r.packed).view(np.uint32), oracle.pack_bits(bits, K))
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 3, 4, 5, 149, 300])
+def test_ragged_tile_counts(q, oracle, luts, n):
+    rng = np.random.default_rng(n)
+    w = rng.standard_normal((n, 256)).astype(np.float32)
+    r = q.encode(torch.from_numpy(w).cuda(), 3, "mcg", want_bits=True)
+    assert r.bits.shape == (n, 256) and r.packed.shape == (n, 24) and r.sse.shape == (n,)
+    if n:
+        m = min(n, 6)                            # the oracle on a few tiles, the rest by self-consistency
+        bits, dq = oracle.viterbi_tb(w[:m], 3, luts["mcg"])
+        assert np.array_equal(_np(r.bits[:m]), bits) and same_bits(_np(r.dq[:m]), dq)
+        one_by_one = torch.cat([q.encode(torch.from_numpy(w[i:i + 1]).cuda(), 3, "mcg").packed for i in range(n - m, n)])
+        assert torch.equal(one_by_one, r.packed[n - m:])                # group size must not change results
+
+
+def test_small_workspace_gives_same_codes(q):
+    torch.manual_seed(5)
+    w = torch.randn(40, 256, device="cuda")
+    full = q.encode(w, 3, "3inst")
+    L = q._lib.lib()
+    ws = torch.empty(int(L.tcq_workspace_min_bytes(3)) * 7 + 4096, dtype=torch.uint8, device="cuda")   # ~7-tile chunks
+    packed = torch.empty(40, 24, dtype=torch.int32, device="cuda")
+    dq = torch.empty(40, 256, device="cuda")
+    rc = L.tcq_encode_tb(w.data_ptr(), 40, 3, 1, packed.data_ptr(), None, dq.data_ptr(), None, ws.data_ptr(), ws.numel(),
+                         torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed, full.packed) and torch.equal(dq, full.dq)
+
+
+def test_c_abi_rejects_bad_arguments_on_device(q):
+    L = q._lib.lib()
+    w = torch.randn(4, 256, device="cuda")
+    packed = torch.empty(4, 24, dtype=torch.int32, device="cuda")
+    ws = torch.empty(int(L.tcq_workspace_bytes(4, 3)), dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.tcq_encode_tb(w.data_ptr(), 4, 3, 2, packed.data_ptr(), None, None, None, ws.data_ptr(), 1024, s) == -6
+    assert L.tcq_encode_tb(w.data_ptr() + 4, 4, 3, 2, packed.data_ptr(), None, None, None, ws.data_ptr(), ws.numel(), s) == -5
+    assert L.tcq_encode_tb(w.data_ptr(), 4, 3, 2, packed.data_ptr(), None, None, None, ws.data_ptr() + 16, ws.numel() - 16, s) == -5
+    assert L.tcq_viterbi_pass(w.data_ptr(), 4, 3, 2, None, 64, packed.data_ptr(), ws.data_ptr(), ws.numel(), s) == -8
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_decode_matches_reference(q, golden, name, K):
+    g = golden["decode"]
+    bits = torch.from_numpy(g[f"K{K}_bits"].astype(np.int64)).cuda()
+    s0 = torch.from_numpy(g[f"K{K}_s0"]).cuda()
+    lut = q.codebook_lut(name, "cuda")
+    assert same_bits(_np(q.decode_recursive(bits, K, lut)), g[f"{name}_K{K}_recursive"])
+    assert same_bits(_np(q.decode_window(bits, K, lut)), g[f"{name}_K{K}_window"])
+    assert same_bits(_np(q.decode_recursive(bits, K, lut, s0)), g[f"{name}_K{K}_recursive_s0"])
+    assert same_bits(_np(q.decode_window(bits, K, name, s0)), g[f"{name}_K{K}_window_s0"])
+
+
+@pytest.mark.parametrize("K", KS)
+def test_pack_and_packed_decode(q, golden, K):
+    enc = golden["encode"]
+    bits = torch.from_numpy(enc[f"mcg_K{K}_bits"].astype(np.int64)).cuda()
+    packed = q.pack_bits(bits, K)
+    assert np.array_equal(_np(packed).view(np.uint32), golden["decode"][f"K{K}_packed"])   # reference pack_bits_np
+    assert same_bits(_np(q.decode_packed(packed, K, "mcg")), enc[f"mcg_K{K}_dq"])           # wrapped decode == encoder dq
+
+
+def test_tailbiting_stream_wraps(q):
+    # tests/test_qtip.py:48-68: exactly K bits per weight, and the symbols alone reproduce dq
+    torch.manual_seed(1)
+    w = torch.randn(4, 256, device="cuda")
+    bits, dq = q.viterbi_tb_b200(w, 2, "mcg")
+    assert bits.shape == (4, 256) and int(bits.max()) < 4 and int(bits.min()) >= 0
+    lut = q.codebook_lut("mcg", "cuda")
+    s = torch.zeros(4, dtype=torch.long, device="cuda")
+    for t in range(256 - 7, 256):
+        s = ((s << 2) | bits[:, t]) & 0xFFFF
+    vals = torch.empty(4, 256, device="cuda")
+    for t in range(256):
+        s = ((s << 2) | bits[:, t]) & 0xFFFF
+        vals[:, t] = lut[s]
+    assert torch.equal(vals, dq)
+
+
+def test_quality_on_gaussian(q):
+    # tests/test_qtip.py:71-83 and the rate-distortion figures of the reference (K=2 ~0.074, K=3 ~0.0185, K=4 ~0.0047)
+    torch.manual_seed(2)
+    w = torch.randn(64, 256, device="cuda")
+    mse = {K: float(q.encode(w, K, "mcg").sse.sum() / w.numel()) for K in KS}
+    assert mse[2] < 0.085 and mse[3] < 0.022 and mse[4] < 0.006
+    assert mse[2] > mse[3] > mse[4]
+
+
+def test_host_tensors_round_trip_through_pinned_memory(q):
+    torch.manual_seed(3)
+    w = torch.randn(9, 256)
+    r_cpu = q.encode(w, 3, "3inst", want_bits=True)
+    r_gpu = q.encode(w.cuda(), 3, "3inst", want_bits=True)
+    assert not r_cpu.packed.is_cuda and not r_cpu.dq.is_cuda
+    assert torch.equal(r_cpu.packed, r_gpu.packed.cpu()) and torch.equal(r_cpu.dq, r_gpu.dq.cpu())
+
+
+def test_encoding_a_reconstruction_is_lossless(q, golden):
+    dq = torch.from_numpy(golden["encode"]["3inst_K3_dq"]).cuda()
+    r = q.encode(dq, 3, "3inst")
+    assert torch.equal(r.dq, dq) and float(r.sse.max()) == 0.0
+
+
+def test_full_size_properties(q):
+    """The second benchmark configuration's size (65 536 tiles, K=3, 3INST): properties that need no oracle."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = torch.randn(65536, 256, generator=g, device="cuda") * 1.2437
+    r = q.encode(w, 3, "3inst")
+    torch.cuda.synchronize()
+    dq = q.decode_packed(r.packed, 3, "3inst")
+    assert torch.equal(dq, r.dq)                                         # encode -> packed -> decode round trip
+    sse = ((w - dq).double() ** 2).sum(dim=1)
+    assert torch.allclose(r.sse.double(), sse, rtol=1e-5)                 # fp32 time-order sum vs fp64 (tolerance: 1e-5 rel)
+    mse = float(sse.sum() / w.numel()) / 1.2437 ** 2
+    assert 0.017 < mse < 0.021                                            # the reference's K=3 distortion, ~0.0188
+    again = q.encode(w[1000:1300], 3, "3inst")                            # any slice re-encodes to the same words
+    assert torch.equal(again.packed, r.packed[1000:1300])
+    idem = q.encode(r.dq[:2048], 3, "3inst")                              # idempotence on reconstructions
+    assert torch.equal(idem.dq, r.dq[:2048]) and float(idem.sse.max()) == 0.0
+
+
+def test_matrix_quantizer_end_to_end(q):
+    # tests/test_qtip.py:95-105: relative MSE of a 2-bit layer stays below 0.12
+    torch.manual_seed(4)
+    w = torch.randn(128, 256, device="cuda") * 0.02
+    wq = q.tcq_quantize_weight(w, K=2, lut=q.codebook_lut("mcg", "cuda"), seed=0, tile_batch=256)
+    rel = float(((w - wq) ** 2).mean() / w.square().mean())
+    assert wq.shape == w.shape and rel < 0.12
+    with pytest.raises(ValueError):
+        q.tcq_quantize_weight(w, K=2, lut="mcg", backend="triton")

@@ -1,0 +1,78 @@
+"""LDLQ on the B200 encoder: the hand-off between the recursion and the tile codec."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from trellis_b200 import ldlq, qtip
+    assert torch.cuda.is_available()
+    return qtip, ldlq
+
+
+def test_teacher_forced_enc_calls_match_reference(mods, golden):
+    """Feed the tiles the reference's enc closure saw; codes and reconstructions must be identical."""
+    q, _ = mods
+    g = golden["ldlq"]
+    assert int(g["n_calls"]) == 16
+    for tiles, bits, dq in zip(g["tiles"], g["bits"], g["dq"]):
+        r = q.encode(torch.from_numpy(tiles).cuda(), 3, "mcg", want_bits=True)
+        assert np.array_equal(r.bits.cpu().numpy(), bits.astype(np.int64))
+        assert same_bits(r.dq.cpu().numpy(), dq)
+
+
+def test_enc_closure_layout(mods, golden):
+    """rows (16 in, n_out) -> tiles -> rows is the reference's index map (ldlq.py:136-143)."""
+    q, l = mods
+    g = golden["ldlq"]
+    tiles = torch.from_numpy(g["tiles"][1]).cuda()                        # what the reference built from its rows
+    rows = l.tiles_to_rows(tiles, 64)                                     # invert with our map ...
+    assert torch.equal(l.rows_to_tiles(rows), tiles)                      # ... and rebuild
+    out = l.make_enc(3, "mcg")(rows)
+    assert out.shape == (16, 64)
+    assert same_bits(l.rows_to_tiles(out).cpu().numpy(), g["dq"][1])
+
+
+def test_zero_feedback_reproduces_plain_quantizer(mods, monkeypatch):
+    """tests/test_ldlq.py:20-51: with L == 0 the LDLQ loop must equal plain TCQ exactly."""
+    q, l = mods
+    torch.manual_seed(0)
+    w = torch.randn(64, 256, device="cuda") * 0.02
+    base = q.tcq_quantize_weight(w, K=3, lut="mcg", seed=0, backend="b200")
+    monkeypatch.setattr(l, "block_ldl", lambda H, b=16: torch.zeros(H.shape[0], H.shape[0], device=H.device))
+    ld = l.tcq_quantize_weight_ldlq(w, K=3, lut="mcg", H=torch.eye(256, device="cuda"), seed=0, sigma_reg=0.0)
+    rel = float(((base - ld) ** 2).mean() / base.square().mean())
+    assert rel < 1e-8
+
+
+def test_feedback_reduces_hessian_objective(mods, golden):
+    """tests/test_ldlq.py:54-72, on the golden matrix and Hessian; also close to the reference's own result."""
+    q, l = mods
+    g = golden["ldlq"]
+    w = torch.from_numpy(g["w"]).cuda()
+    H = torch.from_numpy(g["H"]).cuda()
+    base = q.tcq_quantize_weight(w, K=3, lut="mcg", seed=0)
+    ld = l.tcq_quantize_weight_ldlq(w, K=3, lut="mcg", H=H, seed=0)
+
+    def obj(wq):
+        E = (w - wq).double()
+        return float(torch.einsum("nk,kj,nj->", E, H.double(), E))
+
+    assert obj(ld) < obj(base)
+    ref = torch.from_numpy(g["w_hat"]).cuda()
+    # GPU and CPU GEMMs round differently, and error feedback amplifies that into different
+    # (equally good) codes, so end to end only the objective is comparable: within 5 %.
+    assert abs(obj(ld) - obj(ref)) / obj(ref) < 0.05
+
+
+def test_block_ldl_and_fallback(mods):
+    _, l = mods
+    L0 = l.block_ldl(l.regularize_H(torch.eye(64, device="cuda"), 0.0), b=16)
+    assert torch.allclose(L0, torch.zeros_like(L0), atol=1e-6)
+    bad = torch.full((32, 32), float("nan"), device="cuda")
+    assert l.block_ldl(bad, b=16) is None

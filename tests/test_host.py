@@ -1,0 +1,193 @@
+"""CPU-side checks: the C-ABI library loads and exports what the header declares, argument
+validation, the host logic of LDLQ / incoherence processing, and the multi-rank plumbing (gloo)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+from trellis_b200 import _lib, dist as tdist, ldlq, qtip
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tcq_b200.h")).read()
+    return re.findall(r"TCQ_API[^;(]*?\b(tcq_\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert len(names) >= 11
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} is declared in include/tcq_b200.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signatures and header are out of step"
+    assert _lib.lib().tcq_abi_version() == _lib.ABI_VERSION
+
+
+def test_error_strings_and_workspace_sizes():
+    L = _lib.lib()
+    for code in range(0, -9, -1):
+        assert L.tcq_strerror(code)
+    assert L.tcq_workspace_min_bytes(5) == 0 and L.tcq_workspace_bytes(10, 1) == 0
+    for K, per_tile in ((2, 1 << 20), (3, 768 << 10), (4, 512 << 10)):     # 256 steps x E*K/8 bytes
+        assert per_tile <= L.tcq_workspace_min_bytes(K) < per_tile + 4096
+        assert L.tcq_workspace_bytes(100, K) >= 100 * per_tile
+        assert L.tcq_workspace_bytes(10 ** 7, K) < 8 << 30                # chunked, not proportional to n
+
+
+def test_argument_validation_needs_no_gpu():
+    L = _lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    p += (-p) % 256
+    assert L.tcq_encode_tb(p, 1, 5, 0, p, None, None, None, p, 4096, None) == -1       # K
+    assert L.tcq_encode_tb(p, 1, 3, 7, p, None, None, None, p, 4096, None) == -2       # codebook
+    assert L.tcq_encode_tb(p, -1, 3, 0, p, None, None, None, p, 4096, None) == -3      # count
+    assert L.tcq_encode_tb(None, 1, 3, 0, p, None, None, None, p, 4096, None) == -4    # NULL input
+    assert L.tcq_encode_tb(p + 4, 1, 3, 0, p, None, None, None, p, 4096, None) == -5   # misaligned input
+    assert L.tcq_encode_tb(p, 0, 3, 0, None, None, None, None, None, 0, None) == 0     # empty batch is a no-op
+    assert L.tcq_viterbi_pass(p, 1, 3, 0, None, 7, p, p, 4096, None) == -8             # roll
+    assert L.tcq_decode_packed(None, 1, 3, 0, p, None) == -4
+    assert L.tcq_decode_symbols(p, 1, -1, 3, 0, None, p, None) == -3
+    assert L.tcq_pack_symbols(p, 1, 9, p, None) == -1
+    assert L.tcq_codebook_lut(3, p, None) == -2
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour on a box without a GPU")
+def test_product_path_fails_loudly_without_gpu():
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        qtip.encode(torch.zeros(1, 256), 3, "mcg")
+    with pytest.raises(RuntimeError):
+        qtip.codebook_lut("mcg")
+
+
+def test_encode_rejects_bad_shapes_before_touching_the_device():
+    with pytest.raises(ValueError):
+        qtip.encode(torch.zeros(2, 128), 3, "mcg")
+    with pytest.raises(ValueError):
+        qtip.encode(torch.zeros(2, 256), 5, "mcg")
+    with pytest.raises(ValueError):
+        qtip.pack_bits(torch.zeros(2, 100, dtype=torch.long), 3)
+
+
+def test_tiling_matches_reference_index_map():
+    # qtip.py:288 / :303: tile = (row/16)*(k/16) + col/16, t = (row%16)*16 + col%16
+    n, k = 32, 48
+    z = torch.arange(n * k, dtype=torch.float32).reshape(n, k)
+    tiles = qtip.to_tiles(z)
+    assert tiles.shape == (n // 16 * k // 16, 256)
+    for row, col in ((0, 0), (5, 17), (31, 47), (16, 15)):
+        assert tiles[(row // 16) * (k // 16) + col // 16, (row % 16) * 16 + col % 16] == z[row, col]
+    assert torch.equal(qtip.from_tiles(tiles, n, k), z)
+
+
+def test_incoherence_processing_round_trip():
+    # tests/test_qtip.py:86-92 of the reference
+    torch.manual_seed(3)
+    w = torch.randn(128, 256)
+    ip = qtip.IPContext(w, cb_rms=1.0, seed=0)
+    assert torch.allclose(ip.restore(ip.z), w, atol=1e-5)
+    assert abs(float(ip.z.square().mean().sqrt()) - 1.0) < 1e-4
+    odd = torch.randn(48, 576)                     # 576 = 64 * 9: block shrinks to the largest power-of-two divisor
+    ip2 = qtip.IPContext(odd, cb_rms=1.0, seed=1)
+    assert torch.allclose(ip2.restore(ip2.z), odd, atol=1e-5)
+
+
+def test_block_ldl_identity_and_structure():
+    # tests/test_ldlq.py:12-17
+    L0 = ldlq.block_ldl(ldlq.regularize_H(torch.eye(64), 0.0), b=16)
+    assert torch.allclose(L0, torch.zeros_like(L0), atol=1e-6)
+    torch.manual_seed(0)
+    A = torch.randn(64, 64)
+    H = A.T @ A / 64 + torch.eye(64)
+    Lm = ldlq.block_ldl(H, b=16)
+    for i in range(4):                                                     # diagonal blocks: unit lower triangular minus I
+        blk = Lm[16 * i:16 * i + 16, 16 * i:16 * i + 16]
+        assert torch.allclose(blk, torch.zeros_like(blk), atol=1e-5)
+    assert float(torch.triu(Lm, 1).abs().max()) == 0.0
+    assert ldlq.block_ldl(torch.full((32, 32), float("nan")), b=16) is None
+
+
+def test_ldlq_recursion_with_a_stand_in_quantizer():
+    """With enc = round-to-grid the recursion must satisfy its defining fixed point:
+    every block is the quantisation of (W + L^T (W - Wq)) restricted to later rows."""
+    torch.manual_seed(1)
+    k, n = 256, 32
+    Wt = torch.randn(k, n)
+    A = torch.randn(k, k)
+    Lm = ldlq.block_ldl(A.T @ A / k + torch.eye(k), b=16)
+    enc = lambda rows: torch.round(rows * 4) / 4
+    for buf in (128, 64):
+        Wq = ldlq.ldlq(Wt, Lm, enc, buf=buf)
+        target = Wt + Lm.t() @ (Wt - Wq)
+        assert torch.allclose(Wq, enc(target), atol=0.2501)       # equal up to rounding-boundary flips ...
+        assert float((Wq != enc(target)).float().mean()) < 0.01   # ... which are rare
+    calls = []
+    ldlq.ldlq(Wt, torch.zeros(k, k), lambda r: (calls.append(r.clone()), r)[1])
+    assert len(calls) == k // 16 and torch.equal(calls[0], Wt[k - 16:])   # reverse order, raw targets when L = 0
+
+
+def test_row_block_tiles():
+    rows = torch.arange(16 * 64, dtype=torch.float32).reshape(16, 64)
+    tiles = ldlq.rows_to_tiles(rows)
+    assert tiles.shape == (4, 256)
+    assert tiles[2, 5 * 16 + 3] == rows[3, 2 * 16 + 5]            # t = (out % 16) * 16 + in
+    assert torch.equal(ldlq.tiles_to_rows(tiles, 64), rows)
+
+
+def test_tile_ranges_and_matrix_assignment():
+    for n, world in ((10, 4), (65536, 8), (3, 8), (0, 2)):
+        spans = [tdist.tile_range(n, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= 1
+    plan = tdist.assign_matrices([5, 3, 3, 2, 2, 1], 2)
+    assert sorted(i for p in plan for i in p) == list(range(6))
+    assert abs(sum([5, 3, 3, 2, 2, 1][i] for i in plan[0]) - 8) <= 1
+    shapes = {f"l{i}.{m}": s for i in range(2) for m, s in (("q", (4096, 4096)), ("down", (4096, 12288)))}
+    names = tdist.model_plan(shapes, [n for n in shapes if "down" in n], 2)
+    assert sorted(sum(names, [])) == sorted(shapes)
+
+
+def _gloo_worker(rank, world, port, n_total, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as O                      # CPU stand-in for the encoder, tests only
+        rng = np.random.default_rng(0)
+        w = rng.standard_normal((n_total, 256)).astype(np.float32)
+        lut = O.codebook_lut("mcg")
+
+        def cpu_encoder(tiles, K, codebook):
+            bits, dq = O.viterbi_tb(tiles.numpy(), K, lut, nthreads=1)
+            packed = torch.from_numpy(O.pack_bits(bits, K).view(np.int32))
+            return qtip.Encoded(packed, torch.from_numpy(dq), None, torch.from_numpy(bits))
+
+        every, local, (lo, hi) = tdist.encode_sharded(torch.from_numpy(w), 3, "mcg", encoder=cpu_encoder)
+        only0, _, _ = tdist.encode_sharded(torch.from_numpy(w), 3, "mcg", dst=0, encoder=cpu_encoder)
+        assert (only0 is None) == (rank != 0)
+        assert local.packed.shape[0] == hi - lo
+        torch.save({"all": every, "dst0": only0}, os.path.join(tmp, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_shard_and_gather_over_gloo(tmp_path, oracle, luts):
+    n_total, world = 5, 2                                    # ragged: 3 + 2 tiles
+    port = 29500 + os.getpid() % 2000
+    mp.start_processes(_gloo_worker, args=(world, port, n_total, str(tmp_path)), nprocs=world, join=True,
+                       start_method="spawn")
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((n_total, 256)).astype(np.float32)
+    bits, _ = oracle.viterbi_tb(w, 3, luts["mcg"])
+    want = oracle.pack_bits(bits, 3).view(np.int32)
+    r0 = torch.load(os.path.join(tmp_path, "r0.pt"))
+    r1 = torch.load(os.path.join(tmp_path, "r1.pt"))
+    assert np.array_equal(r0["all"].numpy(), want) and np.array_equal(r1["all"].numpy(), want)
+    assert np.array_equal(r0["dst0"].numpy(), want) and r1["dst0"] is None

@@ -1,0 +1,248 @@
+// C ABI of the B200 trellis codec (declared in include/tcq_b200.h): argument
+// checking, workspace carving, chunking and the launch sequence.  No device
+// memory is allocated or freed here and nothing synchronises with the host.
+#include "../../include/tcq_b200.h"
+
+#include <cstdio>
+#include <cstring>
+
+#include "tcq_forward.cuh"
+#include "tcq_traceback.cuh"
+
+namespace {
+
+using namespace tcq;
+
+thread_local char g_last_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t err, const char* where) {
+    std::snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, cudaGetErrorString(err));
+    return TCQ_E_CUDA;
+}
+
+// SM count of the current device (cached per device ordinal).
+int current_num_sms(int* out) {
+    static int cache[64] = {0};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
+    if (dev >= 0 && dev < 64 && cache[dev] > 0) { *out = cache[dev]; return TCQ_OK; }
+    int sms = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaDeviceGetAttribute");
+    if (dev >= 0 && dev < 64) cache[dev] = sms;
+    *out = sms;
+    return TCQ_OK;
+}
+
+size_t rowb(int K) { return (size_t(1) << (kL - K)) * size_t(K) / 8; }
+size_t bp_bytes_per_tile(int K) { return size_t(kT) * rowb(K); }
+constexpr size_t kAlign = 256;
+size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+// Workspace for `chunk` tiles: backpointers of one whole pass + two int32 hand-off arrays.
+size_t ws_bytes_for_chunk(long long chunk, int K) {
+    return align_up(size_t(chunk) * bp_bytes_per_tile(K)) + 2 * align_up(size_t(chunk) * sizeof(int));
+}
+
+// Tiles per chunk at full speed: eight rounds of the largest tile group on every SM.
+long long default_chunk(int num_sms) { return 8LL * 3 * num_sms; }
+
+struct Workspace {
+    unsigned char* bp;
+    int* e_final;
+    int* overlap;
+    long long chunk;
+};
+
+int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace* out) {
+    if (ws == nullptr) return TCQ_E_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(ws) % kAlign) return TCQ_E_MISALIGNED;
+    long long chunk = n < default_chunk(num_sms) ? n : default_chunk(num_sms);
+    if (ws_bytes_for_chunk(chunk, K) > ws_bytes) {
+        // largest chunk that fits: solve conservatively, then step down
+        chunk = (long long)((ws_bytes > 4 * kAlign ? ws_bytes - 4 * kAlign : 0) / (bp_bytes_per_tile(K) + 2 * sizeof(int)));
+        while (chunk > 0 && ws_bytes_for_chunk(chunk, K) > ws_bytes) --chunk;
+        if (chunk < 1) return TCQ_E_WORKSPACE;
+        // whole rounds of full groups avoid a ragged last wave inside every chunk
+        const long long wave = 3LL * num_sms;
+        if (chunk > wave) chunk = chunk / wave * wave;
+    }
+    unsigned char* base = static_cast<unsigned char*>(ws);
+    out->bp = base;
+    base += align_up(size_t(chunk) * bp_bytes_per_tile(K));
+    out->e_final = reinterpret_cast<int*>(base);
+    base += align_up(size_t(chunk) * sizeof(int));
+    out->overlap = reinterpret_cast<int*>(base);
+    out->chunk = chunk;
+    return TCQ_OK;
+}
+
+cudaError_t forward(int K, int codebook, const ForwardArgs& a, int num_sms, cudaStream_t s) {
+    switch (K) {
+        case 2: return launch_forward<2>(codebook, a, num_sms, s);
+        case 3: return launch_forward<3>(codebook, a, num_sms, s);
+        case 4: return launch_forward<4>(codebook, a, num_sms, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+int check_common(int K, int codebook, long long n) {
+    if (K < 2 || K > 4) return TCQ_E_BAD_K;
+    if (codebook < 0 || codebook > 2) return TCQ_E_BAD_CODEBOOK;
+    if (n < 0) return TCQ_E_BAD_COUNT;
+    return TCQ_OK;
+}
+
+bool misaligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a != 0; }
+
+}  // namespace
+
+extern "C" {
+
+int tcq_abi_version(void) { return 1; }
+
+const char* tcq_strerror(int code) {
+    switch (code) {
+        case TCQ_OK: return "ok";
+        case TCQ_E_BAD_K: return "K must be 2, 3 or 4";
+        case TCQ_E_BAD_CODEBOOK: return "unknown codebook id (0 = 1mad, 1 = 3inst, 2 = mcg)";
+        case TCQ_E_BAD_COUNT: return "negative tile or element count";
+        case TCQ_E_NULL_POINTER: return "a required pointer is NULL";
+        case TCQ_E_MISALIGNED: return "pointer is not aligned as the interface requires";
+        case TCQ_E_WORKSPACE: return "workspace is smaller than tcq_workspace_min_bytes(K)";
+        case TCQ_E_CUDA: return "CUDA runtime error (see tcq_last_cuda_error)";
+        case TCQ_E_BAD_ARGUMENT: return "invalid argument";
+        default: return "unknown error code";
+    }
+}
+
+const char* tcq_last_cuda_error(void) { return g_last_cuda_error; }
+
+size_t tcq_workspace_min_bytes(int K) {
+    if (K < 2 || K > 4) return 0;
+    return ws_bytes_for_chunk(1, K);
+}
+
+size_t tcq_workspace_bytes(int64_t n_tiles, int K) {
+    if (K < 2 || K > 4 || n_tiles < 0) return 0;
+    int num_sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) num_sms = sms;
+    } else {
+        (void)cudaGetLastError();
+    }
+    long long chunk = n_tiles < default_chunk(num_sms) ? n_tiles : default_chunk(num_sms);
+    if (chunk < 1) chunk = 1;
+    return ws_bytes_for_chunk(chunk, K);
+}
+
+int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t* packed, int64_t* bits, float* dq,
+                  float* sse, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_common(K, codebook, n_tiles);
+    if (rc != TCQ_OK) return rc;
+    if (n_tiles == 0) return TCQ_OK;
+    if (w == nullptr || packed == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(w, 16) || misaligned(packed, 4) || (dq && misaligned(dq, 4)) || (bits && misaligned(bits, 8)) ||
+        (sse && misaligned(sse, 4)))
+        return TCQ_E_MISALIGNED;
+    int num_sms = 0;
+    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int nw = kT * K / 32;
+
+    for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
+        const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
+        cudaError_t err;
+        // pass 1: tile rotated by half its length, free start; only the second half of the
+        // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
+        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr};
+        if ((err = forward(K, codebook, f1, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
+        TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, wk.overlap, nullptr, nullptr, nullptr, nullptr};
+        if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
+        // pass 2: true order, start and end tied to the overlap (qtip.py:142)
+        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr};
+        if ((err = forward(K, codebook, f2, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
+        TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, nullptr,
+                         bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
+                         packed + c0 * nw};
+        if ((err = launch_traceback(K, t2, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 2");
+    }
+    return TCQ_OK;
+}
+
+int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const int32_t* overlap, int roll,
+                     int64_t* states, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_common(K, codebook, n_tiles);
+    if (rc != TCQ_OK) return rc;
+    if (roll != 0 && roll != kT / 2) return TCQ_E_BAD_ARGUMENT;
+    if (n_tiles == 0) return TCQ_OK;
+    if (w == nullptr || states == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(w, 16) || misaligned(states, 8) || (overlap && misaligned(overlap, 4))) return TCQ_E_MISALIGNED;
+    int num_sms = 0;
+    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
+        const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
+        cudaError_t err;
+        ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
+                      overlap ? nullptr : wk.e_final, nullptr};
+        if ((err = forward(K, codebook, f, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward");
+        TracebackArgs t{wk.bp, cn, kT, codebook, overlap ? overlap + c0 : wk.e_final, nullptr,
+                        reinterpret_cast<long long*>(states) + c0 * kT, nullptr, nullptr, nullptr};
+        if ((err = launch_traceback(K, t, s)) != cudaSuccess) return cuda_fail(err, "traceback");
+    }
+    return TCQ_OK;
+}
+
+int tcq_decode_packed(const uint32_t* packed, int64_t n_tiles, int K, int codebook, float* dq, void* stream) {
+    int rc = check_common(K, codebook, n_tiles);
+    if (rc != TCQ_OK) return rc;
+    if (n_tiles == 0) return TCQ_OK;
+    if (packed == nullptr || dq == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(packed, 4) || misaligned(dq, 16)) return TCQ_E_MISALIGNED;
+    cudaError_t err = launch_decode_packed(packed, n_tiles, K, codebook, dq, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "decode_packed");
+}
+
+int tcq_decode_symbols(const int64_t* bits, int64_t n, int64_t T, int K, int codebook, const int64_t* s0, float* out,
+                       void* stream) {
+    int rc = check_common(K, codebook, n);
+    if (rc != TCQ_OK) return rc;
+    if (T < 0) return TCQ_E_BAD_COUNT;
+    if (n == 0 || T == 0) return TCQ_OK;
+    if (bits == nullptr || out == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(bits, 8) || misaligned(out, 4) || (s0 && misaligned(s0, 8))) return TCQ_E_MISALIGNED;
+    cudaError_t err = launch_decode_symbols(reinterpret_cast<const long long*>(bits), n, T, K, codebook,
+                                            reinterpret_cast<const long long*>(s0), out,
+                                            static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "decode_symbols");
+}
+
+int tcq_pack_symbols(const int64_t* bits, int64_t n_tiles, int K, uint32_t* packed, void* stream) {
+    if (K < 2 || K > 4) return TCQ_E_BAD_K;
+    if (n_tiles < 0) return TCQ_E_BAD_COUNT;
+    if (n_tiles == 0) return TCQ_OK;
+    if (bits == nullptr || packed == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(bits, 8) || misaligned(packed, 4)) return TCQ_E_MISALIGNED;
+    cudaError_t err = launch_pack_symbols(reinterpret_cast<const long long*>(bits), n_tiles, K, packed,
+                                          static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "pack_symbols");
+}
+
+int tcq_codebook_lut(int codebook, float* lut, void* stream) {
+    if (codebook < 0 || codebook > 2) return TCQ_E_BAD_CODEBOOK;
+    if (lut == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(lut, 4)) return TCQ_E_MISALIGNED;
+    cudaError_t err = launch_codebook_lut(codebook, lut, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "codebook_lut");
+}
+
+}  // extern "C"

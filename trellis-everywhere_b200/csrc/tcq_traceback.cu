@@ -1,0 +1,117 @@
+// Traceback kernel: walks the packed backpointers written by the Viterbi step
+// kernel from the last step to the first and emits, per tile, the state path and
+// everything derived from it (symbols, packed code words, reconstruction).
+//
+// Replaces the host loops of src/trellis/qtip.py:189-196 and
+// src/trellis/viterbi_triton.py:112-116 (256 tiny launches per pass) and fuses the
+// exporter's bit packing (scripts/export_packed_8b.py:52-62).
+//
+// One warp per tile.  The walk itself is a chain of dependent loads:
+//   q_t = bp[t][e_t],  s_t = (q_t << (16-K)) | e_t,  e_{t-1} = s_t >> K .
+// Whatever q_t turns out to be, e_{t-1} is one of only Q edges that share the low
+// bits e_t >> K, so lane j < Q fetches row t-1's entry for candidate q = j while
+// the row-t load is still in flight, and the pick is a shuffle.  That halves the
+// length of the dependent chain (two steps per memory round trip).  Afterwards
+// the 32 lanes turn the 256 states held in shared memory into coalesced outputs.
+#include "tcq_traceback.cuh"
+
+namespace tcq {
+
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+
+template <int K>
+__device__ __forceinline__ uint32_t bp_entry(const unsigned char* row, uint32_t e) {
+    // Edge e's K-bit argmin sits at bit e*K of the row (little endian).  Two byte
+    // loads cover a field that straddles a byte; the second index is clamped so the
+    // last entry of a row never reads past it.
+    constexpr uint32_t Q = Geo<K>::Q, ROWB = Geo<K>::ROWB;
+    const uint32_t bit = e * K;
+    const uint32_t b0 = bit >> 3;
+    const uint32_t b1 = b0 + 1 < ROWB ? b0 + 1 : b0;
+    const uint32_t v = uint32_t(row[b0]) | (uint32_t(row[b1]) << 8);
+    return (v >> (bit & 7)) & (Q - 1);
+}
+
+template <int K>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const TracebackArgs a) {
+    using GE = Geo<K>;
+    constexpr uint32_t Q = GE::Q, E = GE::E, ROWB = GE::ROWB, NW = GE::NWORDS;
+    constexpr int SH = kL - K;                     // q sits above the edge bits
+    constexpr int HB = kL - 2 * K;                 // predecessor edge = (q << HB) | (e >> K)
+
+    __shared__ uint16_t st_all[kWarpsPerCta][kT];
+    const int lane = threadIdx.x & 31;
+    const int wrp = threadIdx.x >> 5;
+    uint16_t* const st = st_all[wrp];
+    const long long tile = (long long)blockIdx.x * kWarpsPerCta + wrp;
+    if (tile >= a.n) return;                       // whole warp leaves together; no block-wide barrier below
+
+    const unsigned char* const bp = a.bp + size_t(tile) * a.bp_steps * ROWB;
+    uint32_t e = uint32_t(a.e_start[tile]) & (E - 1);
+    const int t_off = kT - a.bp_steps;             // row r holds step t = r + t_off
+
+    // ---- the walk: two rows per iteration ----
+    int r = a.bp_steps - 1;
+    for (; r >= 1; r -= 2) {
+        const uint32_t q_hi = lane == 0 ? bp_entry<K>(bp + size_t(r) * ROWB, e) : 0u;
+        const uint32_t cand_e = ((uint32_t(lane) & (Q - 1)) << HB) | (e >> K);
+        const uint32_t q_lo_c = bp_entry<K>(bp + size_t(r - 1) * ROWB, cand_e);   // lanes >= Q repeat lanes < Q
+        const uint32_t q1 = __shfl_sync(0xffffffffu, q_hi, 0);
+        const uint32_t s1 = (q1 << SH) | e;
+        const uint32_t e1 = s1 >> K;                                              // == candidate edge of lane q1
+        const uint32_t q0 = __shfl_sync(0xffffffffu, q_lo_c, int(q1));
+        const uint32_t s0 = (q0 << SH) | e1;
+        if (lane == 0) {
+            st[r + t_off] = uint16_t(s1);
+            st[r - 1 + t_off] = uint16_t(s0);
+        }
+        e = s0 >> K;
+    }
+    if (r == 0) {                                  // odd row count (not used by the encoder, kept for safety)
+        const uint32_t q = __shfl_sync(0xffffffffu, lane == 0 ? bp_entry<K>(bp, e) : 0u, 0);
+        const uint32_t s = (q << SH) | e;
+        if (lane == 0) st[t_off] = uint16_t(s);
+        e = s >> K;
+    }
+    if (lane == 0 && a.e_out != nullptr) a.e_out[tile] = int(e);
+    __syncwarp();
+
+    // ---- outputs over the steps that were walked ----
+    if (a.states != nullptr)
+        for (int t = t_off + lane; t < kT; t += 32) a.states[tile * kT + t] = (long long)st[t];
+    if (a.bits != nullptr)
+        for (int t = t_off + lane; t < kT; t += 32) a.bits[tile * kT + t] = (long long)(st[t] & (Q - 1));
+    if (a.dq != nullptr)
+        for (int t = t_off + lane; t < kT; t += 32) a.dq[tile * kT + t] = cb_value_rt(a.codebook, st[t]);
+    if (a.packed != nullptr && t_off == 0) {
+        // word j holds stream bits 32j .. 32j+31; stream bit p is bit (p % K) of symbol 255 - p / K
+        for (uint32_t j = lane; j < NW; j += 32) {
+            uint32_t word = 0;
+#pragma unroll 8
+            for (uint32_t b = 0; b < 32; ++b) {
+                const uint32_t p = 32 * j + b;
+                const uint32_t t = (kT - 1) - p / K;
+                word |= ((uint32_t(st[t]) >> (p % K)) & 1u) << b;
+            }
+            a.packed[tile * NW + j] = word;
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_traceback(int K, const TracebackArgs& a, cudaStream_t stream) {
+    if (a.n <= 0) return cudaSuccess;
+    const unsigned grid = unsigned((a.n + kWarpsPerCta - 1) / kWarpsPerCta);
+    switch (K) {
+        case 2: tcq_traceback_kernel<2><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
+        case 3: tcq_traceback_kernel<3><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
+        case 4: tcq_traceback_kernel<4><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace tcq

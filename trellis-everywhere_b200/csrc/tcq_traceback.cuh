@@ -1,0 +1,30 @@
+// Arguments of the traceback kernel (see tcq_traceback.cu).
+#pragma once
+
+#include "tcq_common.cuh"
+
+namespace tcq {
+
+struct TracebackArgs {
+    const unsigned char* bp;   // [n][bp_steps][E*K/8] packed backpointers of the LAST bp_steps steps
+    long long n;               // tiles
+    int bp_steps;              // 256 (whole pass) or 128 (second half only)
+    int codebook;              // used for dq
+    const int* e_start;        // [n] edge after the last step (argmin edge, or the forced overlap)
+    int* e_out;                // [n] out: edge BEFORE the first walked step (the overlap when bp_steps = 128), or nullptr
+    long long* states;         // [n,256] out (only the walked steps are written), or nullptr
+    long long* bits;           // [n,256] out: state & (2^K - 1), or nullptr
+    float* dq;                 // [n,256] out: codebook value of each state, or nullptr
+    uint32_t* packed;          // [n,8K] out: exporter word layout (needs bp_steps = 256), or nullptr
+};
+
+cudaError_t launch_traceback(int K, const TracebackArgs& args, cudaStream_t stream);
+
+// Decode / packing kernels (tcq_decode.cu).
+cudaError_t launch_decode_packed(const uint32_t* packed, long long n, int K, int codebook, float* dq, cudaStream_t stream);
+cudaError_t launch_decode_symbols(const long long* bits, long long n, long long T, int K, int codebook,
+                                  const long long* s0, float* out, cudaStream_t stream);
+cudaError_t launch_pack_symbols(const long long* bits, long long n, int K, uint32_t* packed, cudaStream_t stream);
+cudaError_t launch_codebook_lut(int codebook, float* lut, cudaStream_t stream);
+
+}  // namespace tcq

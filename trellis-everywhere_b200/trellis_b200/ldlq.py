@@ -1,0 +1,143 @@
+"""LDLQ error feedback around the B200 tile encoder.
+
+Mirrors ``src/trellis/ldlq.py`` of the reference (same names, arguments and return
+values).  The column-block recursion and its GEMMs stay in PyTorch on the matrix's
+own GPU; the only part that runs in the CUDA extension is what the recursion
+spends its time in, the ``enc`` step (ldlq.py:136-143): a 16-row block of the
+transposed matrix is cut into 256-weight tiles, encoded, and the reconstruction
+is handed back for the error update.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from .qtip import (T_SEQ, CodebookLike, IPContext, _check_backend, _cuda_device, _pow2_block, block_hadamard,
+                   codebook_id, codebook_lut, encode, CODEBOOK_NAMES)
+
+
+def regularize_H(H: torch.Tensor, sigma_reg: float = 0.025) -> torch.Tensor:
+    """H + sigma_reg * mean(diag H) * I  (ldlq.py:24-29)."""
+    out = H.clone()
+    out.diagonal().add_(sigma_reg * torch.diag(H).mean())
+    return out
+
+
+def block_ldl(H: torch.Tensor, b: int = 16) -> Optional[torch.Tensor]:
+    """Block LDL factor of H with b x b unit diagonal blocks, returned with those blocks zeroed.
+
+    Follows ldlq.py:32-70: Cholesky (retried up to 14 times with damping
+    ``2^attempt * 0.01 * max(max|diag H|, 1)`` added to the diagonal of the original
+    H), then every block column is multiplied by the inverse of its diagonal block,
+    and the scalar diagonal is cleared.  Returns None if H never factorises; the
+    caller then quantises without feedback.
+    """
+    k = H.shape[0]
+    if k % b:
+        raise ValueError(f"k={k} not divisible by block {b}")
+    m = k // b
+    damp = max(float(torch.diag(H).abs().max()), 1.0) * 0.01
+    chol = None
+    trial = H
+    for attempt in range(14):
+        chol, info = torch.linalg.cholesky_ex(trial)
+        if int(info) == 0 and bool(torch.isfinite(chol).all()):
+            break
+        chol = None
+        trial = H.clone()
+        trial.diagonal().add_((2.0 ** attempt) * damp)
+    if chol is None:
+        return None
+    blocks = chol.reshape(m, b, m, b)
+    idx = torch.arange(m, device=H.device)
+    dinv = torch.linalg.inv(blocks[idx, :, idx, :])                      # (m, b, b)
+    out = torch.einsum("ibjc,jcd->ibjd", blocks, dinv).reshape(k, k).contiguous()
+    out.diagonal().zero_()
+    return out
+
+
+@torch.no_grad()
+def ldlq(Wt: torch.Tensor, L: torch.Tensor, enc: Callable[[torch.Tensor], torch.Tensor], buf: int = 128) -> torch.Tensor:
+    """Reverse-order block error feedback (ldlq.py:72-99).
+
+    ``Wt (k, n)`` is the transposed matrix in incoherence-processed space, ``L (k, k)``
+    the factor from ``block_ldl``; ``enc`` quantises one compensated ``(16, n)`` row
+    block.  Rows are visited from the last 16-row block to the first; inside a span
+    of ``buf`` rows the correction uses the span's own errors, and after a span is
+    finished its errors are pushed to all earlier rows with one fp32 GEMM.
+    """
+    k, n = Wt.shape
+    src = Wt.float()
+    Lf = L.float()
+    Wq = torch.zeros_like(src)
+    carry = torch.zeros_like(src)          # feedback owed to each row by finished spans (and, in place, by this span)
+    hi = k
+    while hi > 0:
+        lo = max(hi - buf, 0)
+        for bj in range(hi, lo, -16):
+            bi = bj - 16
+            if bj < hi:                                                   # errors of the span's later blocks
+                carry[bi:bj].addmm_(Lf[bj:hi, bi:bj].t(), src[bj:hi] - Wq[bj:hi])
+            Wq[bi:bj] = enc(src[bi:bj] + carry[bi:bj]).float()
+        carry.addmm_(Lf[lo:hi].t(), src[lo:hi] - Wq[lo:hi])
+        hi = lo
+    return Wq.to(Wt.dtype)
+
+
+def _transform_H(H: torch.Tensor, su: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """Bring the input-axis Hessian into incoherence-processed space: signs + block-Hadamard on both sides (ldlq.py:102-109)."""
+    H = su[:, None] * H * su[None, :]
+    return block_hadamard(block_hadamard(H, 0, block), 1, block)
+
+
+def rows_to_tiles(rows: torch.Tensor) -> torch.Tensor:
+    """``(16 in-channels, n_out)`` row block -> ``(n_out/16, 256)`` tiles with t = (out % 16) * 16 + in (ldlq.py:138-140)."""
+    n_out = rows.shape[1]
+    return rows.t().reshape(n_out // 16, T_SEQ).contiguous()
+
+
+def tiles_to_rows(dq: torch.Tensor, n_out: int) -> torch.Tensor:
+    """Inverse of ``rows_to_tiles`` (ldlq.py:142-143)."""
+    return dq.reshape(n_out, 16).t().contiguous()
+
+
+def make_enc(K: int, codebook: CodebookLike, sink: Optional[Callable] = None) -> Callable[[torch.Tensor], torch.Tensor]:
+    """The ``enc`` closure of ldlq.py:136-143 on the B200 encoder.
+
+    ``sink(packed_words)`` (optional) receives each call's packed codes, which is what
+    the reference's exporter captures in its twin closure (export_packed_8b.py:117-125).
+    """
+    cid = codebook_id(codebook)
+
+    def enc(rows: torch.Tensor) -> torch.Tensor:
+        r = encode(rows_to_tiles(rows), K, cid, want_dq=True, want_sse=False)
+        if sink is not None:
+            sink(r.packed)
+        return tiles_to_rows(r.dq, rows.shape[1])
+
+    return enc
+
+
+@torch.no_grad()
+def tcq_quantize_weight_ldlq(w: torch.Tensor, K: int, lut: CodebookLike, H: torch.Tensor, seed: int = 0,
+                             sigma_reg: float = 0.025, dp_dtype=torch.float32, backend: str = "auto") -> torch.Tensor:
+    """LDLQ variant of ``tcq_quantize_weight`` with the signature of ldlq.py:112-154.
+
+    ``w (n_out, k_in)``; ``H (k_in, k_in)`` proxy Hessian in the original space.
+    ``dp_dtype`` is ignored (path metrics are always fp32).
+    """
+    _check_backend(backend)
+    n, k = w.shape
+    if n % 16 or k % 16:
+        raise ValueError(f"shape {tuple(w.shape)} not 16-divisible")
+    dev = _cuda_device(w)
+    lut_t = lut if isinstance(lut, torch.Tensor) else codebook_lut(CODEBOOK_NAMES[codebook_id(lut)], dev)
+    cb_rms = lut_t.float().square().mean().sqrt().item()
+    ip = IPContext(w.to(dev).float(), cb_rms, seed=seed)
+    Ht = _transform_H(H.to(dev).float(), ip.su, block=_pow2_block(k, 128))
+    Lm = block_ldl(regularize_H(Ht, sigma_reg), b=16)
+    if Lm is None:                                  # degenerate Hessian: no feedback for this matrix (ldlq.py:148-151)
+        Lm = torch.zeros(k, k, device=dev)
+    zq_t = ldlq(ip.z.t().contiguous(), Lm, make_enc(K, lut))
+    return ip.restore(zq_t.t().contiguous()).to(dtype=w.dtype, device=w.device)

@@ -1,0 +1,390 @@
+"""Host-side mirror of the reference's tile codec interface, running on the B200 kernels.
+
+Mirrors ``src/trellis/qtip.py`` and ``src/trellis/viterbi_triton.py`` of
+Azimml/trellis-everywhere: same function names, argument meaning and return
+types, so callers switch by changing an import:
+
+    reference                                      this module
+    ---------------------------------------------  -----------------------------------
+    codebook_lut(name, device)      qtip.py:59     codebook_lut(name, device)
+    viterbi_tb(w, K, lut)           qtip.py:124    viterbi_tb_b200(w, K, lut)  /  viterbi_tb
+    viterbi_tb_triton(w, K, lut)    v_triton:121   viterbi_tb_b200(w, K, lut)
+    _viterbi_pass / viterbi_pass_triton            viterbi_pass_b200(w, K, overlap, lut)
+    decode_recursive / decode_window qtip.py:70,82 decode_recursive / decode_window
+    pack_bits_np  export_packed_8b.py:52           pack_bits(bits, K)
+    IPContext                       qtip.py:226    IPContext
+    tcq_quantize_weight             qtip.py:272    tcq_quantize_weight(..., backend="b200")
+
+plus the richer ``encode`` / ``decode_packed`` pair that returns what the kernels
+produce natively (packed code words, reconstruction, per-tile squared error).
+
+The dynamic programme always runs in fp32 and is bit-identical to the reference's
+``viterbi_tb(..., dp_dtype=torch.float32)``.  Everything here needs the CUDA
+extension and a GPU; there is no CPU implementation and no other backend.
+"""
+from __future__ import annotations
+
+from typing import NamedTuple, Optional, Union
+
+import torch
+
+from . import _lib
+
+L = 16
+S = 1 << L
+T_SEQ = 256
+CODEBOOK_IDS = {"1mad": 0, "3inst": 1, "mcg": 2}
+CODEBOOK_NAMES = {v: k for k, v in CODEBOOK_IDS.items()}
+
+CodebookLike = Union[str, int, torch.Tensor]
+
+
+# --------------------------------------------------------------------------- plumbing
+def _cuda_device(t: Optional[torch.Tensor] = None) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("trellis_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+    if t is not None and t.is_cuda:
+        return t.device
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _to_dev(t: torch.Tensor, dev: torch.device, dtype: torch.dtype) -> torch.Tensor:
+    """Contiguous tensor of `dtype` on `dev`; host tensors go through pinned memory."""
+    if t.is_cuda:
+        return t.to(device=dev, dtype=dtype).contiguous()
+    t = t.to(dtype).contiguous()
+    if not t.is_pinned():
+        t = t.pin_memory()
+    return t.to(dev, non_blocking=True)
+
+
+_workspaces: dict = {}
+
+
+def _workspace(dev: torch.device, n_tiles: int, K: int) -> torch.Tensor:
+    """Grow-only scratch per (device, stream): backpointers and per-tile hand-off words."""
+    need = int(_lib.lib().tcq_workspace_bytes(n_tiles, K))
+    key = (dev.index, _stream(dev))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        _workspaces[key] = None          # drop the old block before asking for a larger one
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    """Free the cached scratch buffers."""
+    _workspaces.clear()
+
+
+# --------------------------------------------------------------------------- codebooks
+_lut_cache: dict = {}
+_id_cache: dict = {}
+
+
+def codebook_lut(name: str, device="cpu") -> torch.Tensor:
+    """fp32 value of every 16-bit state, computed by the device codebook functions.
+
+    Same contract as the reference's ``codebook_lut`` (qtip.py:59-66): ``[65536]`` fp32,
+    default device "cpu".  The table is an encode-time convenience for callers that
+    index it; the kernels never read it.
+    """
+    if name not in CODEBOOK_IDS:
+        raise KeyError(name)
+    dev = _cuda_device()
+    key = (name, dev.index)
+    lut = _lut_cache.get(key)
+    if lut is None:
+        lut = torch.empty(S, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().tcq_codebook_lut(CODEBOOK_IDS[name], lut.data_ptr(), _stream(dev)), "tcq_codebook_lut")
+        _lut_cache[key] = lut
+    return lut.to(device).clone()
+
+
+def codebook_id(codebook: CodebookLike) -> int:
+    """Map a codebook name, id or 65536-entry table to the id the kernels take.
+
+    The reference passes the table around as "the codebook"; the kernels compute
+    values from the state number instead, so a table is accepted only if it is
+    bit-identical to one of the three computed codebooks.
+    """
+    if isinstance(codebook, str):
+        if codebook not in CODEBOOK_IDS:
+            raise ValueError(f"unknown codebook {codebook!r}; expected one of {sorted(CODEBOOK_IDS)}")
+        return CODEBOOK_IDS[codebook]
+    if isinstance(codebook, int):
+        if codebook not in CODEBOOK_NAMES:
+            raise ValueError(f"unknown codebook id {codebook}")
+        return codebook
+    if not isinstance(codebook, torch.Tensor) or codebook.numel() != S:
+        raise ValueError("codebook must be a name, an id or a [65536] table")
+    key = (codebook.data_ptr(), str(codebook.device), codebook._version)
+    hit = _id_cache.get(key)
+    if hit is not None:
+        return hit
+    flat = codebook.reshape(-1).float()
+    for name, cid in CODEBOOK_IDS.items():
+        if torch.equal(flat, codebook_lut(name, flat.device)):
+            if len(_id_cache) > 64:
+                _id_cache.clear()
+            _id_cache[key] = cid
+            return cid
+    raise ValueError("table is not one of the computed codebooks (1mad, 3inst, mcg); arbitrary tables are not supported")
+
+
+# --------------------------------------------------------------------------- encode
+class Encoded(NamedTuple):
+    packed: torch.Tensor                 # int32 [n, 8K]: the u32 code words (bit kb of symbol t at bit (255-t)*K+kb)
+    dq: Optional[torch.Tensor]           # fp32 [n, 256] reconstruction
+    sse: Optional[torch.Tensor]          # fp32 [n] squared error per tile
+    bits: Optional[torch.Tensor]         # int64 [n, 256] symbols
+
+
+@torch.no_grad()
+def encode(w: torch.Tensor, K: int, codebook: CodebookLike, *, want_dq: bool = True, want_sse: bool = True,
+           want_bits: bool = False) -> Encoded:
+    """Tail-biting trellis encode of ``w [n, 256]`` (one C-ABI call, no host sync).
+
+    Outputs live on the device of ``w`` (host tensors are staged through pinned
+    memory and the results copied back).
+    """
+    if w.dim() != 2 or w.shape[1] != T_SEQ:
+        raise ValueError(f"expected tiles of shape [n, {T_SEQ}], got {tuple(w.shape)}")
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    cid = codebook_id(codebook)
+    dev = _cuda_device(w)
+    n = w.shape[0]
+    wd = _to_dev(w, dev, torch.float32)
+    packed = torch.empty((n, T_SEQ * K // 32), dtype=torch.int32, device=dev)
+    dq = torch.empty((n, T_SEQ), dtype=torch.float32, device=dev) if want_dq else None
+    sse = torch.empty((n,), dtype=torch.float32, device=dev) if want_sse else None
+    bits = torch.empty((n, T_SEQ), dtype=torch.int64, device=dev) if want_bits else None
+    if n:
+        ws = _workspace(dev, n, K)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_encode_tb(wd.data_ptr(), n, K, cid, packed.data_ptr(),
+                                          bits.data_ptr() if want_bits else None,
+                                          dq.data_ptr() if want_dq else None,
+                                          sse.data_ptr() if want_sse else None,
+                                          ws.data_ptr(), ws.numel(), _stream(dev))
+        _lib.check(rc, "tcq_encode_tb")
+    if not w.is_cuda:
+        packed, dq, sse, bits = (None if x is None else x.cpu() for x in (packed, dq, sse, bits))
+    return Encoded(packed, dq, sse, bits)
+
+
+@torch.no_grad()
+def viterbi_tb_b200(w: torch.Tensor, K: int, lut: CodebookLike):
+    """Drop-in for ``viterbi_tb(w, K, lut)`` / ``viterbi_tb_triton(w, K, lut)``.
+
+    Returns ``(bits int64 [n,256], dq fp32 [n,256])`` exactly as qtip.py:124-144 does
+    with the fp32 dynamic programme.
+    """
+    r = encode(w, K, lut, want_dq=True, want_sse=False, want_bits=True)
+    return r.bits, r.dq
+
+
+def viterbi_tb(w: torch.Tensor, K: int, lut: CodebookLike, dp_dtype=None):
+    """Same signature as the reference's ``viterbi_tb``; ``dp_dtype`` must be None or fp32."""
+    if dp_dtype not in (None, torch.float32):
+        raise ValueError("the B200 encoder computes path metrics in fp32 only")
+    return viterbi_tb_b200(w, K, lut)
+
+
+@torch.no_grad()
+def viterbi_pass_b200(w: torch.Tensor, K: int, overlap: Optional[torch.Tensor], lut: CodebookLike = "mcg",
+                      roll: int = 0) -> torch.Tensor:
+    """Drop-in for ``_viterbi_pass(w, K, lut, overlap)`` / ``viterbi_pass_triton(w, K, overlap)``.
+
+    Returns the optimal state path int64 ``[n, 256]``.  ``roll=128`` runs on
+    ``torch.roll(w, 128, dims=1)`` without materialising it.
+    """
+    if w.dim() != 2 or w.shape[1] != T_SEQ:
+        raise ValueError(f"expected tiles of shape [n, {T_SEQ}], got {tuple(w.shape)}")
+    cid = codebook_id(lut)
+    dev = _cuda_device(w)
+    n = w.shape[0]
+    wd = _to_dev(w, dev, torch.float32)
+    ov = _to_dev(overlap, dev, torch.int32) if overlap is not None else None
+    if ov is not None and ov.shape != (n,):
+        raise ValueError("overlap must have one entry per tile")
+    states = torch.empty((n, T_SEQ), dtype=torch.int64, device=dev)
+    if n:
+        ws = _workspace(dev, n, K)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_viterbi_pass(wd.data_ptr(), n, K, cid, ov.data_ptr() if ov is not None else None,
+                                             roll, states.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev))
+        _lib.check(rc, "tcq_viterbi_pass")
+    return states if w.is_cuda else states.cpu()
+
+
+# --------------------------------------------------------------------------- decode
+@torch.no_grad()
+def decode_packed(packed: torch.Tensor, K: int, codebook: CodebookLike) -> torch.Tensor:
+    """Packed code words ``[n, 8K]`` (int32/uint32) -> reconstruction fp32 ``[n, 256]``."""
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    if packed.dim() != 2 or packed.shape[1] != T_SEQ * K // 32:
+        raise ValueError(f"expected packed words of shape [n, {T_SEQ * K // 32}], got {tuple(packed.shape)}")
+    cid = codebook_id(codebook)
+    dev = _cuda_device(packed)
+    if packed.dtype not in (torch.int32, torch.uint32):
+        raise ValueError("packed words must be int32 or uint32")
+    pd = _to_dev(packed.view(torch.int32), dev, torch.int32)
+    n = pd.shape[0]
+    dq = torch.empty((n, T_SEQ), dtype=torch.float32, device=dev)
+    if n:
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_decode_packed(pd.data_ptr(), n, K, cid, dq.data_ptr(), _stream(dev))
+        _lib.check(rc, "tcq_decode_packed")
+    return dq if packed.is_cuda else dq.cpu()
+
+
+@torch.no_grad()
+def decode_recursive(bits: torch.Tensor, K: int, lut: CodebookLike, s0: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``decode_recursive(bits, K, lut, s0)`` of qtip.py:70-79: symbols ``[n,T]`` -> values ``[n,T]``."""
+    if bits.dim() != 2:
+        raise ValueError("bits must be [n, T]")
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    cid = codebook_id(lut)
+    dev = _cuda_device(bits)
+    bd = _to_dev(bits, dev, torch.int64)
+    sd = _to_dev(s0, dev, torch.int64) if s0 is not None else None
+    n, T = bd.shape
+    out = torch.empty((n, T), dtype=torch.float32, device=dev)
+    if n and T:
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_decode_symbols(bd.data_ptr(), n, T, K, cid, sd.data_ptr() if sd is not None else None,
+                                               out.data_ptr(), _stream(dev))
+        _lib.check(rc, "tcq_decode_symbols")
+    return out if bits.is_cuda else out.cpu()
+
+
+# The reference keeps two formulations (a recursion and a window) and tests that they
+# agree (tests/test_qtip.py:36-45); on the GPU both are the same window kernel.
+decode_window = decode_recursive
+
+
+@torch.no_grad()
+def pack_bits(bits: torch.Tensor, K: int) -> torch.Tensor:
+    """``pack_bits_np(bits, K)`` of the reference's exporter: symbols ``[n,256]`` -> int32 words ``[n, 8K]``."""
+    if bits.dim() != 2 or bits.shape[1] != T_SEQ:
+        raise ValueError(f"expected symbols of shape [n, {T_SEQ}]")
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    dev = _cuda_device(bits)
+    bd = _to_dev(bits, dev, torch.int64)
+    n = bd.shape[0]
+    out = torch.empty((n, T_SEQ * K // 32), dtype=torch.int32, device=dev)
+    if n:
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_pack_symbols(bd.data_ptr(), n, K, out.data_ptr(), _stream(dev))
+        _lib.check(rc, "tcq_pack_symbols")
+    return out if bits.is_cuda else out.cpu()
+
+
+# --------------------------------------------------------------------------- incoherence processing
+def _pow2_block(d: int, cap: int) -> int:
+    """Largest power of two that divides d, at most `cap` (qtip.py:208-213)."""
+    b = 1
+    while b < cap and d % (2 * b) == 0:
+        b *= 2
+    return b
+
+
+def _sylvester(n: int, device, dtype=torch.float32) -> torch.Tensor:
+    """Orthonormal Sylvester-Hadamard matrix of order n (a power of two)."""
+    h = torch.ones((1, 1), device=device, dtype=dtype)
+    while h.shape[0] < n:
+        h = torch.cat((torch.cat((h, h), dim=1), torch.cat((h, -h), dim=1)), dim=0)
+    return h * (n ** -0.5)
+
+
+def block_hadamard(x: torch.Tensor, dim: int, block: int = 128) -> torch.Tensor:
+    """Block-diagonal orthonormal Hadamard along ``dim`` (qtip.py:216-223); its own inverse."""
+    xt = x.movedim(dim, -1)
+    d = xt.shape[-1]
+    b = _pow2_block(d, block)
+    y = xt.reshape(*xt.shape[:-1], d // b, b) @ _sylvester(b, x.device, x.dtype)
+    return y.reshape(xt.shape).movedim(-1, dim)
+
+
+class IPContext:
+    """Incoherence processing around the codec, same recipe and seed use as qtip.py:226-268.
+
+    sign flips on both axes (signs drawn from ``torch.Generator('cpu').manual_seed(seed)``,
+    out axis first), per-output-channel RMS scaling + block-Hadamard over the out axis,
+    per-input-channel RMS scaling + block-Hadamard over the in axis, then one global
+    scale so that ``z`` has the codebook's RMS.  ``restore`` inverts every step.
+    Stays in PyTorch: it is outside the encoder hot path.
+    """
+
+    def __init__(self, w: torch.Tensor, cb_rms: float, seed: int = 0, block: int = 128):
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        n, k = w.shape
+        self.block = block
+        self.sv = (torch.randint(0, 2, (n,), generator=gen).float() * 2 - 1).to(w.device)
+        self.su = (torch.randint(0, 2, (k,), generator=gen).float() * 2 - 1).to(w.device)
+        z = w * self.sv[:, None] * self.su[None, :]
+        out_s = z.square().mean(dim=1).sqrt().clamp_min(1e-8)
+        self.out_s = out_s / out_s.mean()
+        z = block_hadamard(z / self.out_s[:, None], 0, block)
+        in_s = z.square().mean(dim=0).sqrt().clamp_min(1e-8)
+        self.in_s = in_s / in_s.mean()
+        z = block_hadamard(z / self.in_s[None, :], 1, block)
+        self.scale = z.square().mean().sqrt().item() / cb_rms
+        self.z = z / self.scale
+
+    def restore(self, zq: torch.Tensor) -> torch.Tensor:
+        y = block_hadamard(zq * self.scale, 1, self.block) * self.in_s[None, :]
+        y = block_hadamard(y, 0, self.block) * self.out_s[:, None]
+        return y * self.sv[:, None] * self.su[None, :]
+
+
+def to_tiles(z: torch.Tensor) -> torch.Tensor:
+    """``[n, k]`` matrix -> ``[n/16 * k/16, 256]`` tiles of 16 out rows x 16 in columns (qtip.py:288)."""
+    n, k = z.shape
+    return z.reshape(n // 16, 16, k // 16, 16).permute(0, 2, 1, 3).reshape(-1, T_SEQ)
+
+
+def from_tiles(tiles: torch.Tensor, n: int, k: int) -> torch.Tensor:
+    """Inverse of ``to_tiles`` (qtip.py:303)."""
+    return tiles.reshape(n // 16, k // 16, 16, 16).permute(0, 2, 1, 3).reshape(n, k)
+
+
+# --------------------------------------------------------------------------- matrix quantizer
+def _check_backend(backend: str) -> None:
+    if backend not in ("auto", "b200"):
+        raise ValueError(f"backend {backend!r} is not available here: this package has only the B200 CUDA encoder "
+                         "(backend='b200' or 'auto')")
+
+
+@torch.no_grad()
+def tcq_quantize_weight(w: torch.Tensor, K: int, lut: CodebookLike, seed: int = 0, tile_batch: int = 16384,
+                        dp_dtype=torch.float32, backend: str = "auto") -> torch.Tensor:
+    """Fake-quantise one ``[n_out, n_in]`` matrix: incoherence processing + tail-biting TCQ.
+
+    Same signature and result layout as qtip.py:272-304.  ``tile_batch`` is accepted for
+    compatibility (the extension chunks internally); ``dp_dtype`` is ignored because the
+    path metrics are always fp32 (the reference's bit-exact mode).
+    """
+    _check_backend(backend)
+    n, k = w.shape
+    if n % 16 or k % 16:
+        raise ValueError(f"shape {tuple(w.shape)} not 16-divisible")
+    dev = _cuda_device(w)
+    wd = w.to(dev)
+    lut_t = lut if isinstance(lut, torch.Tensor) else codebook_lut(CODEBOOK_NAMES[codebook_id(lut)], dev)
+    cb_rms = lut_t.float().square().mean().sqrt().item()
+    ip = IPContext(wd.float(), cb_rms, seed=seed)
+    tiles = to_tiles(ip.z).contiguous()
+    dq = encode(tiles, K, lut, want_dq=True, want_sse=False).dq
+    return ip.restore(from_tiles(dq, n, k)).to(dtype=w.dtype, device=w.device)
