@@ -24,6 +24,7 @@ extension and a GPU; there is no CPU implementation and no other backend.
 """
 from __future__ import annotations
 
+import weakref
 from typing import NamedTuple, Optional, Union
 
 import torch
@@ -124,16 +125,18 @@ def codebook_id(codebook: CodebookLike) -> int:
         return codebook
     if not isinstance(codebook, torch.Tensor) or codebook.numel() != S:
         raise ValueError("codebook must be a name, an id or a [65536] table")
-    key = (codebook.data_ptr(), str(codebook.device), codebook._version)
+    # Remember the answer per tensor OBJECT (weak reference + version counter): LDLQ hands the
+    # same table to hundreds of encoder calls, and a freed table's address may be reused.
+    key = id(codebook)
     hit = _id_cache.get(key)
-    if hit is not None:
-        return hit
+    if hit is not None and hit[0]() is codebook and hit[1] == codebook._version:
+        return hit[2]
     flat = codebook.reshape(-1).float()
     for name, cid in CODEBOOK_IDS.items():
         if torch.equal(flat, codebook_lut(name, flat.device)):
             if len(_id_cache) > 64:
                 _id_cache.clear()
-            _id_cache[key] = cid
+            _id_cache[key] = (weakref.ref(codebook), codebook._version, cid)
             return cid
     raise ValueError("table is not one of the computed codebooks (1mad, 3inst, mcg); arbitrary tables are not supported")
 
