@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the tail-biting trellis encoder: weights encoded per second (L=16, K=3).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one pass of the hot path over one batch: the tiles of one 4096 x 4096 matrix
+(iid N(0, 0.02^2) with 1 % outliers x20) after randomized-Hadamard incoherence processing,
+i.e. 65 536 independent 256-weight tiles, encoded at K = 3 with the 3INST codebook (packed
+codes, reconstruction and per-tile squared error out).  The matrix is synthetic: seeded
+random values with the shape and distribution the reference's real weights would have.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank encodes its own matrix of
+the same shape (weak scaling: work shards by whole matrices, no exchange during compute)
+and the packed codes are gathered to rank 0 over NCCL inside the timed step.
+
+Printed: ONE JSON line on rank 0 with
+  value     whole-job weights/s with the tiles resident in HBM, timed with CUDA events
+            over exactly K steps between barriers, max over ranks;
+  e2e       the same through the public Python API with HOST tensors (pinned): each step
+            copies the tiles host->device and the results device->host inside the timing;
+  roofline  the Viterbi step kernel alone, timed live with CUDA events through the
+            forward-only entry point, against the fp32/INT lane-issue ceiling;
+  cpu_baseline  the CPU oracle (a C port of the reference's PyTorch dynamic programme)
+            on a bounded sample of the same tiles, all host threads (N = 1 only).
+
+``--impl reference`` times that CPU port alone (rank 0 only) and prints the same kind of line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "trellis-everywhere_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+K_BITS = 3
+CODEBOOK = "3inst"
+MATRIX = (4096, 4096)
+T_SEQ = 256
+STATE_EVALS_PER_WEIGHT = 2 * 65536            # two passes x 2^16 add-compare-select per step
+LANE_OPS_PER_EVAL = 4                         # fsub, fmul, fadd, compare-select: the algorithmic minimum
+WORKLOAD = ("config 2: 4096x4096 fp32 matrix, N(0,0.02^2) + 1% outliers x20, incoherence-processed, "
+            "65536 tiles of 256, K=3, L=16, 3INST")
+
+
+# ------------------------------------------------------------------------------------ helpers
+def measured_peaks() -> dict:
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi (read-only) while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [int(r[0]) for r in self.rows]
+        busy = [c for c in sm if c > 0.5 * max(sm)] or sm
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def make_tiles(torch, qtip, device, seed: int):
+    """The second benchmark configuration's tiles, generated on the device: [65536, 256] fp32."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n, k = MATRIX
+    w = torch.randn(n, k, generator=g, device=device) * 0.02
+    mask = torch.rand(n, k, generator=g, device=device) < 0.01
+    w = torch.where(mask, w * 20, w)
+    lut = qtip.codebook_lut(CODEBOOK, device)
+    ip = qtip.IPContext(w, lut.square().mean().sqrt().item(), seed=0)
+    return qtip.to_tiles(ip.z).contiguous()
+
+
+def cpu_port_rate(tiles_np, seconds: float, threads: int):
+    """Weights/s of the CPU oracle on a bounded sample of `tiles_np`, sized to take about `seconds`."""
+    from oracle import oracle as O
+    lut = O.codebook_lut(CODEBOOK)
+    probe = min(len(tiles_np), max(threads, 8))
+    t0 = time.perf_counter()
+    O.viterbi_tb(tiles_np[:probe], K_BITS, lut, nthreads=threads)
+    per_tile = (time.perf_counter() - t0) / probe
+    n = int(max(probe, min(len(tiles_np), seconds / max(per_tile, 1e-9))))
+    n = max(threads, n // threads * threads)
+    t0 = time.perf_counter()
+    O.viterbi_tb(tiles_np[:n], K_BITS, lut, nthreads=threads)
+    dt = time.perf_counter() - t0
+    return n * T_SEQ / dt, n, dt
+
+
+# ------------------------------------------------------------------------------------ reference arm
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference's CPU implementation of the path (C port, all host threads), rank 0 only."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    O.build()
+    threads = O.max_threads()
+    rng = np.random.default_rng(0)
+    # same distribution as the incoherence-processed tiles: ~N(0, 1.2437^2)
+    sample = max(threads, (args.ref_tiles // threads) * threads)
+    tiles = (rng.standard_normal((sample, T_SEQ)) * 1.2437).astype(np.float32)
+    lut = O.codebook_lut(CODEBOOK)
+    for _ in range(args.warmup):
+        O.viterbi_tb(tiles[:threads], K_BITS, lut, nthreads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.viterbi_tb(tiles, K_BITS, lut, nthreads=threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = sample * T_SEQ / dt
+    line = {
+        "impl": "reference", "metric": "weights encoded/sec (L=16, K=3)", "value": value, "unit": "weights/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "K": K_BITS, "codebook": CODEBOOK, "tiles_per_step": sample},
+        "cpu_baseline": {"value": value, "unit": "weights/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} tiles of the workload's distribution per step (the full 65536 would take "
+                                   f"{65536 * T_SEQ / value / 60:.0f} min)"},
+        "e2e": {"value": value, "unit": "weights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ B200 arm
+def run_b200(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    import torch.distributed as dist
+    from trellis_b200 import _lib, dist as tdist, qtip
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 encoder has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+    cid = qtip.CODEBOOK_IDS[CODEBOOK]
+
+    tiles = make_tiles(torch, qtip, dev, seed=rank)
+    n = tiles.shape[0]
+    nw = T_SEQ * K_BITS // 32
+    gathered = torch.empty((world * n, nw), dtype=torch.int32, device=dev) if world > 1 else None
+
+    def step():
+        r = qtip.encode(tiles, K_BITS, cid, want_dq=True, want_sse=True)
+        if world > 1:                                    # the one collective: packed codes to every rank's buffer
+            dist.all_gather_into_tensor(gathered, r.packed)
+        return r
+
+    def fence():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    ws_bytes = int(lib.tcq_workspace_bytes(n, K_BITS))
+    launches_per_step = int(lib.tcq_encode_launches(n, K_BITS, ws_bytes))
+
+    # ---- device-resident throughput ----
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fence()
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            last = step()
+        e1.record()
+        fence()
+    ms = e0.elapsed_time(e1)
+    mse = float(last.sse.sum() / tiles.numel())
+
+    # ---- end to end: host tensors through the public API ----
+    host = tiles.cpu().pin_memory()
+    h2d = host.numel() * 4
+    d2h = n * nw * 4 + n * T_SEQ * 4 + n * 4
+    qtip.encode(host, K_BITS, cid)                        # warm the pinned staging path
+    fence()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        r_host = qtip.encode(host, K_BITS, cid, want_dq=True, want_sse=True)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, r_host.packed.to(dev, non_blocking=True))
+    fence()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- the step kernel alone (roofline), one chunk per launch exactly as encode uses it ----
+    chunk = min(n, 24 * torch.cuda.get_device_properties(dev).multi_processor_count)
+    ws = qtip._workspace(dev, chunk, K_BITS)
+    ov = torch.randint(0, 1 << (16 - K_BITS), (chunk,), dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    kern_ms = []
+    for overlap, roll, bp_steps in ((None, 128, 128), (ov, 0, 256)):       # pass 1 and pass 2 as the encoder runs them
+        args_c = (tiles.data_ptr(), chunk, K_BITS, cid, overlap.data_ptr() if overlap is not None else None, roll,
+                  bp_steps, ws.data_ptr(), ws.numel(), stream)
+        _lib.check(lib.tcq_forward_pass(*args_c), "tcq_forward_pass")
+        torch.cuda.synchronize(dev)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        k0.record()
+        for _ in range(reps):
+            _lib.check(lib.tcq_forward_pass(*args_c), "tcq_forward_pass")
+        k1.record()
+        torch.cuda.synchronize(dev)
+        kern_ms.append(k0.elapsed_time(k1) / reps)
+
+    # ---- reduce over ranks ----
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(x) for x in times)
+    total_weights = world * n * T_SEQ * args.steps
+
+    line = None
+    if rank == 0:
+        peaks = measured_peaks()
+        props = torch.cuda.get_device_properties(dev)
+        sms = props.multi_processor_count
+        sm_max_mhz = float(peaks.get("sm_max_mhz", 1965.0))
+        peak_lane_ops = sms * 128 * sm_max_mhz * 1e6
+        avg_kernel_ms = sum(kern_ms) / 2
+        evals_per_launch = chunk * T_SEQ * 65536
+        achieved = evals_per_launch * LANE_OPS_PER_EVAL / (avg_kernel_ms * 1e-3)
+        bp_bytes = chunk * (128 + 256) / 2 * (1 << (16 - K_BITS)) * K_BITS / 8      # mean of the two passes
+        ck = clocks.summary()
+        roofline = {
+            "bound": "alu", "kernel": "tcq_forward_kernel<K=3, 3INST>",
+            "achieved": achieved / 1e12, "peak": peak_lane_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_lane_ops,
+            "peak_source": f"{sms} SMs x 128 fp32/int lanes x {sm_max_mhz:.0f} MHz (max SM clock of MEASURED_PEAKS.json"
+                           f"{'' if peaks else '; file absent, nominal clock used'}); the path does no tensor-core or "
+                           "HBM-bound work, so the measured HBM/bf16 peaks do not bound it",
+            "algorithmic": "4 lane-ops (fsub, fmul, fadd, compare-select) x 65536 state evaluations per tile-step",
+            "launch_ms": {"pass1": kern_ms[0], "pass2": kern_ms[1]}, "tiles_per_launch": chunk,
+            "frac_at_sampled_clock": (achieved / (sms * 128 * ck["sm_mhz"] * 1e6)) if ck.get("sm_mhz") else None,
+            "traffic": None,
+            "hbm": {"algorithmic_bytes_per_launch": bp_bytes, "achieved_GBps": bp_bytes / (avg_kernel_ms * 1e-3) / 1e9,
+                    "peak_GBps": peaks.get("hbm_gbs"), "note": "packed backpointer stream, K bits per edge per step"},
+        }
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle as O
+            O.build()
+            threads = O.max_threads()
+            rate, n_s, dt = cpu_port_rate(tiles[:4096].cpu().numpy(), args.cpu_seconds, threads)
+            cpu = {"value": rate, "unit": "weights/s", "cores": threads, "kind": "port",
+                   "sample": f"first {n_s} tiles of the same workload, {dt:.1f} s"}
+        line = {
+            "metric": "weights encoded/sec (L=16, K=3)", "value": total_weights / (ms * 1e-3), "unit": "weights/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "K": K_BITS, "codebook": CODEBOOK, "tiles_per_gpu": n,
+                       "parallelism": f"{world} x whole matrices, NCCL all-gather of packed codes" if world > 1 else "1 GPU",
+                       "l2": "each step streams 2.7 GiB of backpointer scratch, far more than the 126 MB L2, so nothing "
+                             "survives between steps; the 64 MiB of tiles are re-read from HBM"},
+            "e2e": {"value": total_weights / (e2e_ms * 1e-3), "unit": "weights/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": ck, "roofline": roofline, "cpu_baseline": cpu, "mse_z": mse,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
+    ap.add_argument("--ref-tiles", type=int, default=256, help="tiles per step of the reference arm")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        if world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

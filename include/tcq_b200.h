@@ -103,6 +103,25 @@ TCQ_API int tcq_viterbi_pass(const float *w, int64_t n_tiles, int K, int codeboo
                      int64_t *states, void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * The forward sweep of one pass alone (no traceback): runs the Viterbi step kernel
+ * exactly as tcq_encode_tb does for one chunk and leaves the packed backpointers of
+ * the last bp_steps steps (256, or 128 as in the encoder's first pass) in `ws`.
+ * For profiling and roofline measurements of the step kernel; it replaces the
+ * same reference code as tcq_viterbi_pass (src/trellis/qtip.py:177-182,
+ * src/trellis/viterbi_triton.py:24-78).  n_tiles must fit one chunk of the
+ * workspace (otherwise TCQ_E_WORKSPACE).
+ */
+TCQ_API int tcq_forward_pass(const float *w, int64_t n_tiles, int K, int codebook, const int32_t *overlap, int roll,
+                             int bp_steps, void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Number of kernel launches tcq_encode_tb issues for n_tiles with a workspace of
+ * ws_bytes (four per chunk: step kernel and traceback for each of the two passes),
+ * or a negative TCQ_E_* code.  No reference counterpart; used for accounting.
+ */
+TCQ_API int64_t tcq_encode_launches(int64_t n_tiles, int K, size_t ws_bytes);
+
+/*
  * Decode packed tiles: dq[i,t] = codebook(16-bit window at bit (255-t)*K of tile
  * i's words, wrapping past the last word).  Replaces lut[states2]
  * (src/trellis/qtip.py:144), the wrapped-stream decode of tests/test_qtip.py:55-67

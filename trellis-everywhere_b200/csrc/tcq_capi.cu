@@ -40,9 +40,13 @@ size_t bp_bytes_per_tile(int K) { return size_t(kT) * rowb(K); }
 constexpr size_t kAlign = 256;
 size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
-// Workspace for `chunk` tiles: backpointers of one whole pass + two int32 hand-off arrays.
+constexpr int kMaxKeys = 4;   // partial minima per tile left by the cluster kernel (one per CTA of a cluster)
+
+// Workspace for `chunk` tiles: backpointers of one whole pass, two int32 hand-off arrays and the
+// per-CTA partial minima of the final metrics.
 size_t ws_bytes_for_chunk(long long chunk, int K) {
-    return align_up(size_t(chunk) * bp_bytes_per_tile(K)) + 2 * align_up(size_t(chunk) * sizeof(int));
+    return align_up(size_t(chunk) * bp_bytes_per_tile(K)) + 2 * align_up(size_t(chunk) * sizeof(int)) +
+           align_up(size_t(chunk) * kMaxKeys * sizeof(unsigned long long));
 }
 
 // Tiles per chunk at full speed: eight rounds of the largest tile group on every SM.
@@ -52,6 +56,7 @@ struct Workspace {
     unsigned char* bp;
     int* e_final;
     int* overlap;
+    unsigned long long* keys;
     long long chunk;
 };
 
@@ -61,7 +66,7 @@ int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace*
     long long chunk = n < default_chunk(num_sms) ? n : default_chunk(num_sms);
     if (ws_bytes_for_chunk(chunk, K) > ws_bytes) {
         // largest chunk that fits: solve conservatively, then step down
-        chunk = (long long)((ws_bytes > 4 * kAlign ? ws_bytes - 4 * kAlign : 0) / (bp_bytes_per_tile(K) + 2 * sizeof(int)));
+        chunk = (long long)((ws_bytes > 4 * kAlign ? ws_bytes - 4 * kAlign : 0) / (bp_bytes_per_tile(K) + 2 * sizeof(int) + kMaxKeys * sizeof(unsigned long long)));
         while (chunk > 0 && ws_bytes_for_chunk(chunk, K) > ws_bytes) --chunk;
         if (chunk < 1) return TCQ_E_WORKSPACE;
         // whole rounds of full groups avoid a ragged last wave inside every chunk
@@ -74,15 +79,18 @@ int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace*
     out->e_final = reinterpret_cast<int*>(base);
     base += align_up(size_t(chunk) * sizeof(int));
     out->overlap = reinterpret_cast<int*>(base);
+    base += align_up(size_t(chunk) * sizeof(int));
+    out->keys = reinterpret_cast<unsigned long long*>(base);
     out->chunk = chunk;
     return TCQ_OK;
 }
 
-cudaError_t forward(int K, int codebook, const ForwardArgs& a, int num_sms, cudaStream_t s) {
+cudaError_t forward(int K, int codebook, const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t s,
+                    int* nkeys) {
     switch (K) {
-        case 2: return launch_forward<2>(codebook, a, num_sms, s);
-        case 3: return launch_forward<3>(codebook, a, num_sms, s);
-        case 4: return launch_forward<4>(codebook, a, num_sms, s);
+        case 2: return launch_forward<2>(codebook, a, keys, num_sms, s, nkeys);
+        case 3: return launch_forward<3>(codebook, a, keys, num_sms, s, nkeys);
+        case 4: return launch_forward<4>(codebook, a, keys, num_sms, s, nkeys);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -160,14 +168,16 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
         cudaError_t err;
         // pass 1: tile rotated by half its length, free start; only the second half of the
         // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
-        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr};
-        if ((err = forward(K, codebook, f1, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
-        TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, wk.overlap, nullptr, nullptr, nullptr, nullptr};
+        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f};
+        int nkeys = 0;
+        if ((err = forward(K, codebook, f1, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
+        TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, nkeys ? wk.keys : nullptr, nkeys, wk.overlap,
+                         nullptr, nullptr, nullptr, nullptr};
         if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
         // pass 2: true order, start and end tied to the overlap (qtip.py:142)
-        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr};
-        if ((err = forward(K, codebook, f2, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
-        TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, nullptr,
+        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f};
+        if ((err = forward(K, codebook, f2, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
+        TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, 0, nullptr, nullptr,
                          bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
                          packed + c0 * nw};
         if ((err = launch_traceback(K, t2, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 2");
@@ -193,13 +203,47 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
         cudaError_t err;
         ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
-                      overlap ? nullptr : wk.e_final, nullptr};
-        if ((err = forward(K, codebook, f, num_sms, s)) != cudaSuccess) return cuda_fail(err, "forward");
-        TracebackArgs t{wk.bp, cn, kT, codebook, overlap ? overlap + c0 : wk.e_final, nullptr,
+                      overlap ? nullptr : wk.e_final, nullptr, 1.0f};
+        int nkeys = 0;
+        if ((err = forward(K, codebook, f, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
+        const bool use_keys = overlap == nullptr && nkeys > 0;
+        TracebackArgs t{wk.bp, cn, kT, codebook, overlap ? overlap + c0 : wk.e_final, use_keys ? wk.keys : nullptr, nkeys, nullptr,
                         reinterpret_cast<long long*>(states) + c0 * kT, nullptr, nullptr, nullptr};
         if ((err = launch_traceback(K, t, s)) != cudaSuccess) return cuda_fail(err, "traceback");
     }
     return TCQ_OK;
+}
+
+int tcq_forward_pass(const float* w, int64_t n_tiles, int K, int codebook, const int32_t* overlap, int roll,
+                     int bp_steps, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_common(K, codebook, n_tiles);
+    if (rc != TCQ_OK) return rc;
+    if ((roll != 0 && roll != kT / 2) || (bp_steps != kT && bp_steps != kT / 2)) return TCQ_E_BAD_ARGUMENT;
+    if (n_tiles == 0) return TCQ_OK;
+    if (w == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(w, 16) || (overlap && misaligned(overlap, 4))) return TCQ_E_MISALIGNED;
+    int num_sms = 0;
+    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
+    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f};
+    int nkeys = 0;
+    cudaError_t err = forward(K, codebook, f, wk.keys, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "forward");
+}
+
+int64_t tcq_encode_launches(int64_t n_tiles, int K, size_t ws_bytes) {
+    if (K < 2 || K > 4) return TCQ_E_BAD_K;
+    if (n_tiles < 0) return TCQ_E_BAD_COUNT;
+    if (n_tiles == 0) return 0;
+    int num_sms = 0;
+    int rc = current_num_sms(&num_sms);
+    if (rc != TCQ_OK) return rc;
+    Workspace wk;
+    alignas(256) static unsigned char dummy[256];          // carve() only does pointer arithmetic on it
+    if ((rc = carve(dummy, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    return 4 * ((n_tiles + wk.chunk - 1) / wk.chunk);
 }
 
 int tcq_decode_packed(const uint32_t* packed, int64_t n_tiles, int K, int codebook, float* dq, void* stream) {

@@ -61,9 +61,11 @@ __device__ __forceinline__ float cb_from_x(uint32_t x) {
         return __fmaf_rn(res, r, a);
     } else {
         const uint32_t v = (x & 0x8FFF8FFFu) ^ 0x3B603B60u;
-        const __half2 h = *reinterpret_cast<const __half2*>(&v);
-        const float2 f = __half22float2(h);
-        return __fadd_rn(f.y, f.x);
+        // fp32(hi) + lo with the mixed-precision add of sm_100 (fp16 operand widened in the adder):
+        // one instruction less than two conversions and an add; the sum is exact either way.
+        float r;
+        asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 fh;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.f32.f16 fh, hi;\n\tadd.rn.f32.f16 %0, lo, fh;\n\t}" : "=f"(r) : "r"(v));
+        return r;
     }
 }
 
@@ -84,6 +86,86 @@ __device__ __forceinline__ float cb_value_rt(int cb, uint32_t state) {
 __device__ __forceinline__ float cand_cost(float w, float v, float c) {
     const float d = __fsub_rn(w, v);
     return __fadd_rn(__fmul_rn(d, d), c);
+}
+
+// ---- Blackwell packed-fp32 arithmetic -------------------------------------------------
+// sm_100 executes add/sub/mul on two fp32 values held in a 64-bit register pair as ONE
+// instruction (each half is an ordinary IEEE round-to-nearest operation, no flush to
+// zero).  The fp32 lanes are not wider for it, but it costs one issue slot instead of
+// two, and issue slots are what bounds the Viterbi step kernel.
+using f32x2 = unsigned long long;
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// Candidates of two predecessors at once: fl(fl(fl(w - v) * fl(w - v)) + c) per half.
+// The final addition is written as fma(product, one2, c) with one2 = {1.0f, 1.0f} passed in
+// at run time.  ptxas contracts a packed multiply that feeds a packed add into one fused
+// multiply-add (single rounding) even when both carry .rn and -fmad=false is given, which
+// changes path metrics by an ulp; a product that enters an fma as the MULTIPLICAND cannot
+// be contracted, and x * 1 + c rounds exactly like x + c.
+__device__ __forceinline__ f32x2 cand_cost2(f32x2 w2, f32x2 v2, f32x2 c2, f32x2 one2) {
+    const f32x2 d = sub2(w2, v2);
+    return fma2(mul2(d, d), one2, c2);
+}
+
+// Three-input minimum (one instruction on sm_100).
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+template <int N> __device__ __forceinline__ float min_of(const float (&c)[N]);
+template <> __device__ __forceinline__ float min_of<4>(const float (&c)[4]) { return fminf(min3(c[0], c[1], c[2]), c[3]); }
+template <> __device__ __forceinline__ float min_of<8>(const float (&c)[8]) {
+    return min3(min3(c[0], c[1], c[2]), min3(c[3], c[4], c[5]), fminf(c[6], c[7]));
+}
+template <> __device__ __forceinline__ float min_of<16>(const float (&c)[16]) {
+    const float a = min3(min3(c[0], c[1], c[2]), min3(c[3], c[4], c[5]), min3(c[6], c[7], c[8]));
+    const float b = min3(min3(c[9], c[10], c[11]), min3(c[12], c[13], c[14]), c[15]);
+    return fminf(a, b);
+}
+
+// Conditional move "if (c == best) tag = value", the argmin scan's inner operation.
+// Compare/select instructions issue at half the rate of fp32 arithmetic on sm_100, and the
+// scan has one compare per candidate already, so the moves alternate between the two pipes:
+//   * odd q: an ordinary select (compare/select pipe);
+//   * even q: tag = c * zero + value as a predicated fma on the candidate itself, with
+//     zero = 0.0f passed in at run time, which executes on the fp32 multiply-add pipe.  (It
+//     must depend on a loop-varying register: one * value would be hoisted as a constant and
+//     leave a predicated register move on the compare/select pipe.)  c is finite, so
+//     c * 0 + value == value exactly.
+__device__ __forceinline__ void take_if_equal_fma(float& tag, float c, float best, float zero, float value) {
+    asm("{\n\t.reg .pred p;\n\tsetp.eq.f32 p, %1, %2;\n\t@p fma.rn.f32 %0, %1, %3, %4;\n\t}" : "+f"(tag) : "f"(c), "f"(best), "f"(zero), "f"(value));
+}
+__device__ __forceinline__ void take_if_equal_balanced(int q, float& tag, float c, float best, float zero, float value) {
+    if (q & 1) tag = (c == best) ? value : tag;
+    else take_if_equal_fma(tag, c, best, zero, value);
 }
 
 }  // namespace tcq

@@ -22,6 +22,14 @@
 //     computes;
 //   * one __syncthreads per step.
 //
+// Inner loop, per (successor, tile): the Q candidates are formed two at a time with
+// packed fp32 sub/mul/add (f32x2), their minimum with three-input min, and the argmin
+// as "lowest q whose candidate equals the minimum" with conditional moves, split between
+// the compare/select pipe and the fp32 pipe, that build argmin * 2^(l*K) as an exact float;
+// the tags of an item's successors are summed and converted to the packed backpointer bits once.  Per candidate that is about 1.5
+// (arithmetic) + 0.5 (min) + 2 (compare, conditional move) issue slots, plus the
+// shared codebook evaluation.
+//
 // Shared memory: 2*G*E*4 + 2*G*E*K/8 + G*1024 bytes (K=3, G=3: 217 KiB of the
 // 227 KiB a CTA may use).
 #pragma once
@@ -39,6 +47,7 @@ struct ForwardArgs {
     unsigned char* bp;       // [n][bp_steps][E*K/8] packed backpointers
     int* e_final;            // [n] out: argmin edge of the final metrics (lowest index on ties), or nullptr
     float* final_cost;       // [n] out: final metric at overlap[tile] (constrained) / its minimum, or nullptr
+    float one;               // must be 1.0f: run-time multiplier of the predicated-FMUL conditional move
 };
 
 template <int K, int G>
@@ -69,6 +78,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
     const bool constrained = a.overlap != nullptr;
     const int t_store0 = kT - a.bp_steps;
     const float kInf = __uint_as_float(kInfBits);
+    const f32x2 one2 = pack2(a.one, a.one);
+    const float zero = a.one - 1.0f;
 
     for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
         const long long tile0 = grp * G;
@@ -92,9 +103,12 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
 
         int cur = 0;
         for (int t = 0; t < kT; ++t) {
-            float wt[G];
+            f32x2 w2[G];
 #pragma unroll
-            for (int g = 0; g < G; ++g) wt[g] = wv[g * kT + ((t + a.roll) & (kT - 1))];
+            for (int g = 0; g < G; ++g) {
+                const float wt = wv[g * kT + ((t + a.roll) & (kT - 1))];
+                w2[g] = pack2(wt, wt);
+            }
 
             // ---- stream the previous step's backpointer rows to HBM (128-bit, coalesced) ----
             if (t > t_store0) {
@@ -120,39 +134,45 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
                 const int lc = it / HN;
                 const int e0 = h * Q + lc * LU;                 // first successor edge of the item
 
-                float cin[G][Q];
+                // predecessor metrics, paired (q, q+1) for the packed arithmetic
+                f32x2 cin2[G][Q / 2];
 #pragma unroll
                 for (int g = 0; g < G; ++g)
 #pragma unroll
-                    for (int q = 0; q < Q; ++q) cin[g][q] = cin_base[g * E + q * HN + h];
+                    for (int j = 0; j < Q / 2; ++j)
+                        cin2[g][j] = pack2(cin_base[g * E + (2 * j) * HN + h], cin_base[g * E + (2 * j + 1) * HN + h]);
 
                 const uint32_t xb = uint32_t(e0) * MUL + ADD;   // scrambled word of state (q=0, e0)
                 float outv[G][LU];
-                uint32_t args[G];
+                float tags[G];                                  // sum_l argmin_l * 2^(l*K), exact in fp32 (< 2^24)
 #pragma unroll
-                for (int g = 0; g < G; ++g) args[g] = 0u;
+                for (int g = 0; g < G; ++g) tags[g] = 0.0f;
 
 #pragma unroll
                 for (int lu = 0; lu < LU; ++lu) {
-                    float v[Q];
+                    // codebook values of the Q predecessors' states, once for all G tiles
+                    f32x2 v2[Q / 2];
 #pragma unroll
-                    for (int q = 0; q < Q; ++q) v[q] = cb_from_x<CB>(xb + uint32_t(q * E + lu) * MUL);
+                    for (int j = 0; j < Q / 2; ++j)
+                        v2[j] = pack2(cb_from_x<CB>(xb + uint32_t((2 * j) * E + lu) * MUL),
+                                      cb_from_x<CB>(xb + uint32_t((2 * j + 1) * E + lu) * MUL));
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
-                        float best = cand_cost(wt[g], v[0], cin[g][0]);
-                        uint32_t arg = 0u;
+                        float c[Q];
 #pragma unroll
-                        for (int q = 1; q < Q; ++q) {
-                            const float c = cand_cost(wt[g], v[q], cin[g][q]);
-                            if (c < best) {            // strict: the lowest q wins ties
-                                best = c;
-                                arg = uint32_t(q) << (lu * K);
-                            }
-                        }
+                        for (int j = 0; j < Q / 2; ++j) unpack2(cand_cost2(w2[g], v2[j], cin2[g][j], one2), c[2 * j], c[2 * j + 1]);
+                        const float best = min_of<Q>(c);
+                        // lowest q whose candidate equals the minimum (== first minimum, as torch.min)
+                        float tag = float((Q - 1) << (lu * K));
+#pragma unroll
+                        for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced(q, tag, c[q], best, zero, float(q << (lu * K)));
                         outv[g][lu] = best;
-                        args[g] |= arg;
+                        tags[g] = __fadd_rn(tags[g], tag);
                     }
                 }
+                uint32_t args[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) args[g] = __float2uint_rz(tags[g]);
 
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
@@ -233,7 +253,10 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
 
 // Host-side launcher for one (K, codebook): picks the tiles-per-CTA variant.
 // Implemented once per K in tcq_forward_k{2,3,4}.cu.
+// `keys` ([n][4] 64-bit scratch) enables the cluster kernel; *nkeys is then the number of
+// per-CTA partial minima written per tile (0: the single-CTA kernel ran and wrote e_final).
 template <int K>
-cudaError_t launch_forward(int codebook, const ForwardArgs& args, int num_sms, cudaStream_t stream);
+cudaError_t launch_forward(int codebook, const ForwardArgs& args, unsigned long long* keys, int num_sms,
+                           cudaStream_t stream, int* nkeys);
 
 }  // namespace tcq

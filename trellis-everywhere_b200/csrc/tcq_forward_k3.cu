@@ -4,12 +4,30 @@
 namespace tcq {
 
 namespace {
-constexpr int kNT = 256;   // threads per CTA
-constexpr int kLU = 8;     // successors per work item
-constexpr int kGMax = 3;   // most tiles one CTA advances together (shared-memory bound)
+constexpr int kNT = 512;     // threads per CTA
+constexpr int kLU = 8;       // successors per work item, single-CTA kernel
+constexpr int kGMax = 3;     // most tiles one CTA advances together (shared-memory bound)
+constexpr int kCLU4 = 4;     // successors per work item with 4 CTAs per cluster (32 codebook values per thread)
+constexpr int kCLU2 = 8;     // ... with 2 CTAs per cluster (64 codebook values per thread)
 
 template <int CB>
-cudaError_t launch_cb(const ForwardArgs& a, int num_sms, cudaStream_t stream) {
+cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t stream, int* nkeys) {
+    *nkeys = 0;
+    const int csize = cluster_size_choice();
+    if (keys != nullptr && csize != 0) {
+        const bool two_sets = pick_cluster_set(a.n, num_sms, csize) == 2;
+        cudaError_t err;
+        if (csize == 2)
+            err = two_sets ? launch_cluster_variant<3, CB, 2, 2, kNT, kCLU2>(a, keys, stream)
+                           : launch_cluster_variant<3, CB, 2, 1, kNT, kCLU2>(a, keys, stream);
+        else
+            err = two_sets ? launch_cluster_variant<3, CB, 4, 2, kNT, kCLU4>(a, keys, stream)
+                           : launch_cluster_variant<3, CB, 4, 1, kNT, kCLU4>(a, keys, stream);
+        if (err != cudaErrorNotSupported) {
+            *nkeys = csize;
+            return err;
+        }
+    }
     switch (pick_group<kGMax>(a.n, num_sms)) {
         case 1: return launch_variant<3, CB, 1, kNT, kLU>(a, num_sms, stream);
         case 2: return launch_variant<3, CB, 2, kNT, kLU>(a, num_sms, stream);
@@ -20,11 +38,12 @@ cudaError_t launch_cb(const ForwardArgs& a, int num_sms, cudaStream_t stream) {
 }  // namespace
 
 template <>
-cudaError_t launch_forward<3>(int codebook, const ForwardArgs& a, int num_sms, cudaStream_t stream) {
+cudaError_t launch_forward<3>(int codebook, const ForwardArgs& a, unsigned long long* keys, int num_sms,
+                               cudaStream_t stream, int* nkeys) {
     switch (codebook) {
-        case kCb1Mad:  return launch_cb<kCb1Mad>(a, num_sms, stream);
-        case kCb3Inst: return launch_cb<kCb3Inst>(a, num_sms, stream);
-        case kCbMcg:   return launch_cb<kCbMcg>(a, num_sms, stream);
+        case kCb1Mad:  return launch_cb<kCb1Mad>(a, keys, num_sms, stream, nkeys);
+        case kCb3Inst: return launch_cb<kCb3Inst>(a, keys, num_sms, stream, nkeys);
+        case kCbMcg:   return launch_cb<kCbMcg>(a, keys, num_sms, stream, nkeys);
         default:       return cudaErrorInvalidValue;
     }
 }

@@ -3,9 +3,14 @@
 // so that the large kernels compile in parallel.
 #pragma once
 
-#include "tcq_forward.cuh"
+#include <cstdlib>
+#include <cstring>
+
+#include "tcq_forward_cluster.cuh"
 
 namespace tcq {
+
+constexpr int kDefaultClusterSize = 2;
 
 template <int K, int CB, int G, int NT, int LU>
 static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_t stream) {
@@ -17,6 +22,64 @@ static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_
     const int grid = int(ngroups < num_sms ? ngroups : num_sms);
     kern<<<grid, NT, smem, stream>>>(a);
     return cudaGetLastError();
+}
+
+// Cluster form.  Returns cudaErrorNotSupported (and launches nothing) if this device cannot
+// co-schedule a cluster of C CTAs with the kernel's shared-memory footprint.
+template <int K, int CB, int C, int GS, int NT, int LU>
+static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, cudaStream_t stream) {
+    auto kern = tcq_forward_cluster_kernel<K, CB, C, GS, NT, LU>;
+    constexpr size_t smem = cluster_smem_bytes<K, C, GS>();
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (err != cudaSuccess) return err;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = C;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(NT);
+    cfg.gridDim = dim3(C);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    static int max_clusters[64] = {0};            // per device ordinal; 0 = not queried yet, -1 = unsupported
+    int dev = 0;
+    if ((err = cudaGetDevice(&dev)) != cudaSuccess) return err;
+    int maxc = dev >= 0 && dev < 64 ? max_clusters[dev] : 0;
+    if (maxc == 0) {
+        int q = 0;
+        err = cudaOccupancyMaxActiveClusters(&q, kern, &cfg);
+        if (err != cudaSuccess) { (void)cudaGetLastError(); q = 0; }
+        maxc = q > 0 ? q : -1;
+        if (dev >= 0 && dev < 64) max_clusters[dev] = maxc;
+    }
+    if (maxc < 0) return cudaErrorNotSupported;
+    constexpr int G = 2 * GS;
+    const long long ngroups = (a.n + G - 1) / G;
+    const long long ncl = ngroups < maxc ? ngroups : maxc;
+    cfg.gridDim = dim3(unsigned(ncl * C));
+    ClusterArgs ca{a, keys};
+    return cudaLaunchKernelEx(&cfg, kern, ca);
+}
+
+// Tile sets of one tile (2 tiles per cluster) finish a small batch sooner when there are
+// fewer groups of 4 than clusters; otherwise sets of two amortise the per-step overheads.
+static inline int pick_cluster_set(long long n, int num_sms, int C) {
+    const long long clusters = num_sms / C > 0 ? num_sms / C : 1;
+    return (n + 3) / 4 >= clusters ? 2 : 1;
+}
+
+// Which step kernel runs: TCQ_FORWARD_KERNEL = "cta" (single-CTA kernel), "cluster2" or
+// "cluster4" (cluster kernel with that many CTAs per cluster).  Returns 0, 2 or 4.
+static inline int cluster_size_choice() {
+    const char* v = std::getenv("TCQ_FORWARD_KERNEL");
+    if (v == nullptr) return kDefaultClusterSize;
+    if (std::strcmp(v, "cta") == 0) return 0;
+    if (std::strcmp(v, "cluster2") == 0) return 2;
+    if (std::strcmp(v, "cluster4") == 0) return 4;
+    return kDefaultClusterSize;
 }
 
 // Relative time of one group of G tiles: G tiles of add-compare-select work plus

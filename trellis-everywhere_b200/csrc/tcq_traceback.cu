@@ -49,7 +49,17 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const 
     if (tile >= a.n) return;                       // whole warp leaves together; no block-wide barrier below
 
     const unsigned char* const bp = a.bp + size_t(tile) * a.bp_steps * ROWB;
-    uint32_t e = uint32_t(a.e_start[tile]) & (E - 1);
+    uint32_t e;
+    if (a.keys != nullptr) {            // argmin of the final metrics, left as per-CTA partial minima by the cluster kernel
+        unsigned long long k = a.keys[tile * a.nkeys];
+        for (int i = 1; i < a.nkeys; ++i) {
+            const unsigned long long o = a.keys[tile * a.nkeys + i];
+            k = o < k ? o : k;
+        }
+        e = uint32_t(k) & (E - 1);
+    } else {
+        e = uint32_t(a.e_start[tile]) & (E - 1);
+    }
     const int t_off = kT - a.bp_steps;             // row r holds step t = r + t_off
 
     // ---- the walk: two rows per iteration ----

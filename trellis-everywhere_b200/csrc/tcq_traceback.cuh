@@ -10,7 +10,9 @@ struct TracebackArgs {
     long long n;               // tiles
     int bp_steps;              // 256 (whole pass) or 128 (second half only)
     int codebook;              // used for dq
-    const int* e_start;        // [n] edge after the last step (argmin edge, or the forced overlap)
+    const int* e_start;        // [n] edge after the last step (argmin edge, or the forced overlap); or nullptr with `keys`
+    const unsigned long long* keys;  // [n][nkeys] partial minima (metric bits << 32 | edge) whose smallest gives the start edge
+    int nkeys;
     int* e_out;                // [n] out: edge BEFORE the first walked step (the overlap when bp_steps = 128), or nullptr
     long long* states;         // [n,256] out (only the walked steps are written), or nullptr
     long long* bits;           // [n,256] out: state & (2^K - 1), or nullptr

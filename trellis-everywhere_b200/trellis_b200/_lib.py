@@ -25,6 +25,8 @@ SIGNATURES = {
     "tcq_workspace_min_bytes": (_sz, [_int]),
     "tcq_encode_tb": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "tcq_viterbi_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
+    "tcq_forward_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _int, _vp, _sz, _vp]),
+    "tcq_encode_launches": (_i64, [_i64, _int, _sz]),
     "tcq_decode_packed": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
     "tcq_decode_symbols": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "tcq_pack_symbols": (_int, [_vp, _i64, _int, _vp, _vp]),
