@@ -13,7 +13,7 @@ constexpr int kCLU2 = 8;     // ... with 2 CTAs per cluster (64 codebook values 
 template <int CB>
 cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t stream, int* nkeys) {
     *nkeys = 0;
-    const int csize = cluster_size_choice();
+    const int csize = cluster_size_choice(a.n, num_sms, /*always_cluster=*/false);
     if (keys != nullptr && csize != 0) {
         const bool two_sets = pick_cluster_set(a.n, num_sms, csize) == 2;
         cudaError_t err;

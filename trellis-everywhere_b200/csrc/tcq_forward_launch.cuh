@@ -10,8 +10,6 @@
 
 namespace tcq {
 
-constexpr int kDefaultClusterSize = 2;
-
 template <int K, int CB, int G, int NT, int LU>
 static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_t stream) {
     auto kern = tcq_forward_kernel<K, CB, G, NT, LU>;
@@ -71,15 +69,19 @@ static inline int pick_cluster_set(long long n, int num_sms, int C) {
     return (n + 3) / 4 >= clusters ? 2 : 1;
 }
 
-// Which step kernel runs: TCQ_FORWARD_KERNEL = "cta" (single-CTA kernel), "cluster2" or
-// "cluster4" (cluster kernel with that many CTAs per cluster).  Returns 0, 2 or 4.
-static inline int cluster_size_choice() {
+// Which step kernel runs for a launch of n tiles.  Returns the cluster size (2 or 4) or 0 for
+// the single-CTA kernel.  Default: 2-CTA clusters once there is a full round of 4-tile groups
+// for every cluster (always for K = 2, where the single-CTA kernel can hold only one tile per
+// SM and so shares no codebook work); below that the single-CTA kernel's smaller groups finish
+// a small batch sooner.  TCQ_FORWARD_KERNEL = cta | cluster2 | cluster4 overrides (comparison runs).
+static inline int cluster_size_choice(long long n, int num_sms, bool always_cluster) {
     const char* v = std::getenv("TCQ_FORWARD_KERNEL");
-    if (v == nullptr) return kDefaultClusterSize;
-    if (std::strcmp(v, "cta") == 0) return 0;
-    if (std::strcmp(v, "cluster2") == 0) return 2;
-    if (std::strcmp(v, "cluster4") == 0) return 4;
-    return kDefaultClusterSize;
+    if (v != nullptr) {
+        if (std::strcmp(v, "cta") == 0) return 0;
+        if (std::strcmp(v, "cluster2") == 0) return 2;
+        if (std::strcmp(v, "cluster4") == 0) return 4;
+    }
+    return (always_cluster || n >= 4LL * (num_sms / 2)) ? 2 : 0;
 }
 
 // Relative time of one group of G tiles: G tiles of add-compare-select work plus
