@@ -52,6 +52,7 @@ extern "C" {
 #define TCQ_E_WORKSPACE (-6)     /* workspace smaller than tcq_workspace_min_bytes() */
 #define TCQ_E_CUDA (-7)          /* CUDA runtime error (no device, launch failure) */
 #define TCQ_E_BAD_ARGUMENT (-8)  /* other invalid argument (roll, T, ...) */
+#define TCQ_E_TOO_MANY_TILES (-9) /* batch larger than tcq_encode_tb_static_max_tiles(K) */
 
 /* Version of this ABI (bumped on any signature change). */
 TCQ_API int tcq_abi_version(void);
@@ -101,6 +102,25 @@ TCQ_API int tcq_encode_tb(const float *w, int64_t n_tiles, int K, int codebook, 
  */
 TCQ_API int tcq_viterbi_pass(const float *w, int64_t n_tiles, int K, int codebook, const int32_t *overlap, int roll,
                      int64_t *states, void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * tcq_encode_tb for callers that cannot allocate device memory (no counterpart in the
+ * reference, which allocates its scratch with torch.empty on every call).
+ * Same inputs, outputs and results as tcq_encode_tb, but no workspace argument: the
+ * backpointer scratch is a fixed TCQ_STATIC_SCRATCH_BYTES array inside the library's device
+ * image, so the call performs no cudaMalloc / cudaFree and uses no allocating library.
+ *   - at most tcq_encode_tb_static_max_tiles(K) tiles per call (31 / 42 / 63 for K = 2 / 3 / 4);
+ *     more returns TCQ_E_TOO_MANY_TILES and launches nothing;
+ *   - every GPU context that loads the library holds the array until the process exits;
+ *   - the first call on a device resolves the array's address (cudaGetSymbolAddress, with
+ *     that device current); make it before any stream capture begins;
+ *   - all calls share the array: calls that may overlap on the GPU must be serialised by
+ *     the caller.  Nothing needs clearing between calls.
+ */
+#define TCQ_STATIC_SCRATCH_BYTES (32u << 20)
+TCQ_API int64_t tcq_encode_tb_static_max_tiles(int K);
+TCQ_API int tcq_encode_tb_static(const float *w, int64_t n_tiles, int K, int codebook, uint32_t *packed, int64_t *bits,
+                                 float *dq, float *sse, void *stream);
 
 /*
  * The forward sweep of one pass alone (no traceback): runs the Viterbi step kernel

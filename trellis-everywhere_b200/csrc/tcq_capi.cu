@@ -108,7 +108,7 @@ bool misaligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p)
 
 extern "C" {
 
-int tcq_abi_version(void) { return 1; }
+int tcq_abi_version(void) { return 2; }
 
 const char* tcq_strerror(int code) {
     switch (code) {
@@ -121,6 +121,7 @@ const char* tcq_strerror(int code) {
         case TCQ_E_WORKSPACE: return "workspace is smaller than tcq_workspace_min_bytes(K)";
         case TCQ_E_CUDA: return "CUDA runtime error (see tcq_last_cuda_error)";
         case TCQ_E_BAD_ARGUMENT: return "invalid argument";
+        case TCQ_E_TOO_MANY_TILES: return "more tiles than the static scratch holds (see tcq_encode_tb_static_max_tiles)";
         default: return "unknown error code";
     }
 }
