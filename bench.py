@@ -184,6 +184,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     cid = qtip.CODEBOOK_IDS[CODEBOOK]
 
     tiles = make_tiles(torch, qtip, dev, seed=rank)
+    if args.tiles:                                       # reduced case for profiler captures; not the benchmark
+        tiles = tiles[:args.tiles].contiguous()
     n = tiles.shape[0]
     nw = T_SEQ * K_BITS // 32
     gathered = torch.empty((world * n, nw), dtype=torch.int32, device=dev) if world > 1 else None
@@ -271,7 +273,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         bp_bytes = chunk * (128 + 256) / 2 * (1 << (16 - K_BITS)) * K_BITS / 8      # mean of the two passes
         ck = clocks.summary()
         roofline = {
-            "bound": "alu", "kernel": "tcq_forward_kernel<K=3, 3INST>",
+            "bound": "alu", "kernel": "Viterbi step kernel (tcq_forward_cluster_kernel<K=3, 3INST, 2 CTAs>)",
             "achieved": achieved / 1e12, "peak": peak_lane_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_lane_ops,
             "peak_source": f"{sms} SMs x 128 fp32/int lanes x {sm_max_mhz:.0f} MHz (max SM clock of MEASURED_PEAKS.json"
                            f"{'' if peaks else '; file absent, nominal clock used'}); the path does no tensor-core or "
@@ -295,7 +297,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "metric": "weights encoded/sec (L=16, K=3)", "value": total_weights / (ms * 1e-3), "unit": "weights/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "K": K_BITS, "codebook": CODEBOOK, "tiles_per_gpu": n,
+            "config": {"workload": WORKLOAD if not args.tiles else f"REDUCED to {n} tiles (profiling case) of: " + WORKLOAD,
+                       "K": K_BITS, "codebook": CODEBOOK, "tiles_per_gpu": n,
                        "parallelism": f"{world} x whole matrices, NCCL all-gather of packed codes" if world > 1 else "1 GPU",
                        "l2": "each step streams 2.7 GiB of backpointer scratch, far more than the 126 MB L2, so nothing "
                              "survives between steps; the 64 MiB of tiles are re-read from HBM"},
@@ -320,6 +323,9 @@ def main() -> None:
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
     ap.add_argument("--ref-tiles", type=int, default=256, help="tiles per step of the reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tiles", type=int, default=0,
+                    help="encode only the first N tiles of the workload (small cases for ncu captures; the printed line "
+                         "is then not a benchmark result)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -76,3 +76,29 @@ def test_block_ldl_and_fallback(mods):
     assert torch.allclose(L0, torch.zeros_like(L0), atol=1e-6)
     bad = torch.full((32, 32), float("nan"), device="cuda")
     assert l.block_ldl(bad, b=16) is None
+
+
+def test_model_level_encode_packs_in_reference_tile_order(mods, tmp_path):
+    """encode_matrix / encode_model: the packed words alone reproduce W_hat, for plain and LDLQ matrices, and a
+    second run resumes from the files of the first."""
+    q, l = mods
+    from trellis_b200 import model
+    shapes = {"model.layers.0.self_attn.q_proj": (64, 256), "model.layers.0.mlp.down_proj": (64, 256)}
+    hess = lambda name, k, dev: model.synthetic_hessian(name, k, dev, rows=512)
+    logs = []
+    res, gathered = model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, out_dir=str(tmp_path), log=logs.append)
+    assert set(gathered) == set(shapes) and len(logs) == 2
+    assert res["model.layers.0.mlp.down_proj"]["ldlq"] and not res["model.layers.0.self_attn.q_proj"]["ldlq"]
+    for name, (n, k) in shapes.items():
+        w = model.synthetic_weight(name, (n, k), torch.device("cuda"))
+        H = hess(name, k, w.device) if model.is_mlp(name) else None
+        packed, w_hat, rel = model.encode_matrix(w, 3, "mcg", model.seed_of(name), H)
+        assert torch.equal(packed, gathered[name]) and packed.shape == (n // 16 * k // 16, 24)
+        lut = q.codebook_lut("mcg", "cuda")
+        ip = q.IPContext(w, lut.square().mean().sqrt().item(), seed=model.seed_of(name))
+        zq = q.from_tiles(q.decode_packed(packed, 3, "mcg"), n, k)        # tile order (row/16)*(k/16)+col/16
+        assert torch.equal(ip.restore(zq), w_hat)
+        assert rel < 0.05
+    res2, gathered2 = model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, out_dir=str(tmp_path))
+    assert all(r["skipped"] for r in res2.values())
+    assert all(torch.equal(gathered2[n], gathered[n]) for n in shapes)

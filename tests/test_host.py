@@ -191,3 +191,33 @@ def test_two_rank_shard_and_gather_over_gloo(tmp_path, oracle, luts):
     r1 = torch.load(os.path.join(tmp_path, "r1.pt"))
     assert np.array_equal(r0["all"].numpy(), want) and np.array_equal(r1["all"].numpy(), want)
     assert np.array_equal(r0["dst0"].numpy(), want) and r1["dst0"] is None
+
+
+def _gloo_model_gather_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from trellis_b200 import model
+        shapes = {f"model.layers.{i}.{m}": s for i in range(2)
+                  for m, s in (("self_attn.q_proj", (32, 64)), ("mlp.up_proj", (96, 32)), ("mlp.down_proj", (32, 96)))}
+        ldlq_names = [n for n in shapes if model.is_mlp(n)]
+        mine = tdist.model_plan(shapes, ldlq_names, world)[rank]
+        # stand-in code words: a pattern that encodes (matrix, tile, word) so misplaced rows are caught
+        names = sorted(shapes)
+        fake = lambda n: (torch.arange((shapes[n][0] // 16) * (shapes[n][1] // 16) * 24, dtype=torch.int32).reshape(-1, 24)
+                          + 100000 * names.index(n))
+        got = model.gather_model_codes(shapes, ldlq_names, {n: fake(n) for n in mine}, 3, world, rank, torch.device("cpu"))
+        if rank == 0:
+            assert set(got) == set(shapes)
+            assert all(torch.equal(got[n], fake(n)) for n in shapes)
+            open(os.path.join(tmp, "ok"), "w").write("ok")
+        else:
+            assert got is None
+    finally:
+        dist.destroy_process_group()
+
+
+def test_model_code_gather_over_gloo(tmp_path):
+    port = 31500 + os.getpid() % 2000
+    mp.start_processes(_gloo_model_gather_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True, start_method="spawn")
+    assert os.path.exists(os.path.join(tmp_path, "ok"))
