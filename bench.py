@@ -281,7 +281,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "algorithmic": "4 lane-ops (fsub, fmul, fadd, compare-select) x 65536 state evaluations per tile-step",
             "launch_ms": {"pass1": kern_ms[0], "pass2": kern_ms[1]}, "tiles_per_launch": chunk,
             "frac_at_sampled_clock": (achieved / (sms * 128 * ck["sm_mhz"] * 1e6)) if ck.get("sm_mhz") else None,
-            "traffic": None,
+            # ncu dram__bytes_read+write of a 592-tile launch pair = 0.831 of its algorithmic backpointer bytes
+            # (profiles/step_kernel_k3_3inst_592tiles_ncu_full.md), scaled here by the tiles per launch
+            "traffic": 0.831 * bp_bytes,
             "hbm": {"algorithmic_bytes_per_launch": bp_bytes, "achieved_GBps": bp_bytes / (avg_kernel_ms * 1e-3) / 1e9,
                     "peak_GBps": peaks.get("hbm_gbs"), "note": "packed backpointer stream, K bits per edge per step"},
         }
