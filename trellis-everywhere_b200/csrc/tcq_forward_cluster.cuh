@@ -41,7 +41,11 @@ constexpr size_t cluster_smem_bytes() {
 }
 
 // Split-phase hardware cluster barrier (all threads of all CTAs of the cluster take part).
+#ifdef TCQ_X_RELAXED
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+#else
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+#endif
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 struct ClusterArgs {
@@ -102,7 +106,11 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         const int qn = e0 / HN, hn = e0 % HN;              // role of e0 in the next step: predecessor qn of butterfly hn
         const int owner = hn / HNC;
         float* local = cost + qn * HNC + (hn % HNC);
+#ifdef TCQ_X_LOCAL
+        dst[i] = local;
+#else
         dst[i] = owner == rank ? local : cluster.map_shared_rank(local, owner);
+#endif
         const uint32_t xb = uint32_t(e0) * MUL + ADD;
 #pragma unroll
         for (int lu = 0; lu < LU; ++lu)
@@ -187,6 +195,9 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // stream one step's row slices of tile set `s` (written during step t) to HBM
     auto flush_set = [&](int s, int t, long long tile0) {
         if (t < t_store0) return;
+#ifdef TCQ_X_NOFLUSH
+        if (t >= 0) return;
+#endif
         const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(t & 1) * G * ROWBC + size_t(s) * GS * ROWBC);
         constexpr int V = ROWBC / 16;
         for (int i = tid; i < GS * V; i += NT) {
