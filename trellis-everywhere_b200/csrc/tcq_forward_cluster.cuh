@@ -124,8 +124,29 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     const long long nclusters = gridDim.x / C;
     const long long cluster_id = blockIdx.x / C;
 
+    long long tile0 = 0;                           // first tile of the group being processed
+
+    // stream one step's row slices of tile set `s` (written during step t) to HBM (coalesced 128-bit stores)
+    auto flush_set = [&](int s, int t, long long tile0) {
+        if (t < t_store0) return;
+#ifdef TCQ_X_NOFLUSH
+        if (t >= 0) return;
+#endif
+        const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(t & 1) * G * ROWBC + size_t(s) * GS * ROWBC);
+        constexpr int V = ROWBC / 16;
+        for (int i = tid; i < GS * V; i += NT) {
+            const int gg = i / V, cc = i - gg * V;
+            const long long tile = tile0 + s * GS + gg;
+            if (tile < a.n) {
+                uint4* d = reinterpret_cast<uint4*>(a.bp + (size_t(tile) * a.bp_steps + (t - t_store0)) * ROWB + size_t(rank) * ROWBC);
+                d[cc] = src[i];
+            }
+        }
+    };
+
     // one add-compare-select step of tile set `s` (tiles s*GS .. s*GS+GS-1), reading buffer `cur`
-    // (`arrive_mid`: open the pending barrier phase half way through, see the main loop)
+    // (`arrive_mid`: half way through, open the pending barrier phase and then stream the set's
+    // previous rows to HBM; see the main loop)
     auto step_set = [&](int s, int t, int cur, bool arrive_mid) {
         f32x2 w2[GS];
 #pragma unroll
@@ -149,7 +170,10 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
             for (int gg = 0; gg < GS; ++gg) tags[gg] = 0.0f;
 #pragma unroll
             for (int lu = 0; lu < LU; ++lu) {
-                if (i == NI / 2 && lu == (NI > 1 ? 0 : LU / 2) && arrive_mid) cluster_arrive();
+                if (i == NI / 2 && lu == (NI > 1 ? 0 : LU / 2) && arrive_mid) {
+                    cluster_arrive();
+                    if (t > 0) flush_set(s, t - 1, tile0);
+                }
 #pragma unroll
                 for (int gg = 0; gg < GS; ++gg) {
                     float c[Q];
@@ -192,26 +216,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         }
     };
 
-    // stream one step's row slices of tile set `s` (written during step t) to HBM
-    auto flush_set = [&](int s, int t, long long tile0) {
-        if (t < t_store0) return;
-#ifdef TCQ_X_NOFLUSH
-        if (t >= 0) return;
-#endif
-        const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(t & 1) * G * ROWBC + size_t(s) * GS * ROWBC);
-        constexpr int V = ROWBC / 16;
-        for (int i = tid; i < GS * V; i += NT) {
-            const int gg = i / V, cc = i - gg * V;
-            const long long tile = tile0 + s * GS + gg;
-            if (tile < a.n) {
-                uint4* d = reinterpret_cast<uint4*>(a.bp + (size_t(tile) * a.bp_steps + (t - t_store0)) * ROWB + size_t(rank) * ROWBC);
-                d[cc] = src[i];
-            }
-        }
-    };
-
     for (long long grp = cluster_id; grp < ngroups; grp += nclusters) {
-        const long long tile0 = grp * G;
+        tile0 = grp * G;
         // ---- weights and initial metrics (src/trellis/qtip.py:161-165) ----
         for (int i = tid; i < G * kT; i += NT) {
             const long long tile = tile0 + (i >> 8);
@@ -233,22 +239,23 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         // Two tile sets alternate, and the barrier phase that publishes one set's step is opened
         // (arrive) HALF WAY THROUGH the other set's next step and closed (wait) at its end:
         //   * the arrive carries release semantics, i.e. it waits for this thread's earlier
-        //     stores (remote shared memory, backpointer rows) to be performed; half a step
-        //     later they long are, so the fence costs nothing;
+        //     stores (remote shared memory, backpointer rows) to be performed.  The rows of the
+        //     set's previous step are therefore streamed to HBM right AFTER the arrive, a whole
+        //     step before the next one, so that no fence ever finds them in flight;
         //   * the second half of the step covers the barrier's own latency.
-        // A set's staging rows of step t are streamed to HBM after the phase of step t is closed
-        // and before the arrive that allows step t+2 to overwrite them.
+        // Staging rows of set s, step t-1 are read in the middle of its step t: after the phase
+        // that published them closed, and before the arrive (middle of the other set's next step)
+        // of the phase that lets step t+1 overwrite them.
         step_set(0, 0, 0, false);
         for (int t = 0; t < kT; ++t) {
             const int cur = t & 1;
-            if (t > 0) flush_set(1, t - 1, tile0);
-            step_set(1, t, cur, true);       // arrives for "set 0, step t" on the way
+            step_set(1, t, cur, true);       // middle: arrive for "set 0, step t", then stream set 1's step t-1
             cluster_wait();                  // set 0, step t: complete in every CTA
-            flush_set(0, t, tile0);
-            if (t + 1 < kT) step_set(0, t + 1, cur ^ 1, true);   // arrives for "set 1, step t" on the way
-            else cluster_arrive();
+            if (t + 1 < kT) step_set(0, t + 1, cur ^ 1, true);   // middle: arrive for "set 1, step t", stream set 0's step t
+            else { cluster_arrive(); }
             cluster_wait();                  // set 1, step t: complete in every CTA
         }
+        flush_set(0, kT - 1, tile0);
         flush_set(1, kT - 1, tile0);
 
         // ---- final metrics live in buffer 0 (256 steps), layout [Q][HNC] = edges q*HN + rank*HNC + hl ----
