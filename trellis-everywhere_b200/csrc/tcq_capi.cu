@@ -46,7 +46,7 @@ constexpr int kMaxKeys = 4;   // partial minima per tile left by the cluster ker
 // per-CTA partial minima of the final metrics.
 size_t ws_bytes_for_chunk(long long chunk, int K) {
     return align_up(size_t(chunk) * bp_bytes_per_tile(K)) + 2 * align_up(size_t(chunk) * sizeof(int)) +
-           align_up(size_t(chunk) * kMaxKeys * sizeof(unsigned long long));
+           align_up(size_t(chunk) * kMaxKeys * sizeof(unsigned long long)) + kAlign /* status word */;
 }
 
 // Tiles per chunk at full speed: eight rounds of the largest tile group on every SM.
@@ -57,6 +57,7 @@ struct Workspace {
     int* e_final;
     int* overlap;
     unsigned long long* keys;
+    unsigned int* status;
     long long chunk;
 };
 
@@ -66,7 +67,7 @@ int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace*
     long long chunk = n < default_chunk(num_sms) ? n : default_chunk(num_sms);
     if (ws_bytes_for_chunk(chunk, K) > ws_bytes) {
         // largest chunk that fits: solve conservatively, then step down
-        chunk = (long long)((ws_bytes > 4 * kAlign ? ws_bytes - 4 * kAlign : 0) / (bp_bytes_per_tile(K) + 2 * sizeof(int) + kMaxKeys * sizeof(unsigned long long)));
+        chunk = (long long)((ws_bytes > 5 * kAlign ? ws_bytes - 5 * kAlign : 0) / (bp_bytes_per_tile(K) + 2 * sizeof(int) + kMaxKeys * sizeof(unsigned long long)));
         while (chunk > 0 && ws_bytes_for_chunk(chunk, K) > ws_bytes) --chunk;
         if (chunk < 1) return TCQ_E_WORKSPACE;
         // whole rounds of full groups avoid a ragged last wave inside every chunk
@@ -81,16 +82,17 @@ int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace*
     out->overlap = reinterpret_cast<int*>(base);
     base += align_up(size_t(chunk) * sizeof(int));
     out->keys = reinterpret_cast<unsigned long long*>(base);
+    base += align_up(size_t(chunk) * kMaxKeys * sizeof(unsigned long long));
+    out->status = reinterpret_cast<unsigned int*>(base);
     out->chunk = chunk;
     return TCQ_OK;
 }
 
-cudaError_t forward(int K, int codebook, const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t s,
-                    int* nkeys) {
+cudaError_t forward(int K, int codebook, const ForwardArgs& a, const Workspace& wk, int num_sms, cudaStream_t s, int* nkeys) {
     switch (K) {
-        case 2: return launch_forward<2>(codebook, a, keys, num_sms, s, nkeys);
-        case 3: return launch_forward<3>(codebook, a, keys, num_sms, s, nkeys);
-        case 4: return launch_forward<4>(codebook, a, keys, num_sms, s, nkeys);
+        case 2: return launch_forward<2>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
+        case 3: return launch_forward<3>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
+        case 4: return launch_forward<4>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -121,6 +123,7 @@ const char* tcq_strerror(int code) {
         case TCQ_E_WORKSPACE: return "workspace is smaller than tcq_workspace_min_bytes(K)";
         case TCQ_E_CUDA: return "CUDA runtime error (see tcq_last_cuda_error)";
         case TCQ_E_BAD_ARGUMENT: return "invalid argument";
+        case TCQ_E_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up; the outputs of that call are invalid";
         case TCQ_E_TOO_MANY_TILES: return "more tiles than the static scratch holds (see tcq_encode_tb_static_max_tiles)";
         default: return "unknown error code";
     }
@@ -163,6 +166,7 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
     if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int nw = kT * K / 32;
+    if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
 
     for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
@@ -171,13 +175,13 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
         // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
         ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f};
         int nkeys = 0;
-        if ((err = forward(K, codebook, f1, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
+        if ((err = forward(K, codebook, f1, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
         TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, nkeys ? wk.keys : nullptr, nkeys, wk.overlap,
                          nullptr, nullptr, nullptr, nullptr};
         if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
         // pass 2: true order, start and end tied to the overlap (qtip.py:142)
         ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f};
-        if ((err = forward(K, codebook, f2, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
+        if ((err = forward(K, codebook, f2, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
         TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, 0, nullptr, nullptr,
                          bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
                          packed + c0 * nw};
@@ -199,6 +203,7 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     Workspace wk;
     if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
 
     for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
@@ -206,7 +211,7 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
         ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
                       overlap ? nullptr : wk.e_final, nullptr, 1.0f};
         int nkeys = 0;
-        if ((err = forward(K, codebook, f, wk.keys, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
+        if ((err = forward(K, codebook, f, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
         const bool use_keys = overlap == nullptr && nkeys > 0;
         TracebackArgs t{wk.bp, cn, kT, codebook, overlap ? overlap + c0 : wk.e_final, use_keys ? wk.keys : nullptr, nkeys, nullptr,
                         reinterpret_cast<long long*>(states) + c0 * kT, nullptr, nullptr, nullptr};
@@ -228,10 +233,27 @@ int tcq_forward_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     Workspace wk;
     if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
     if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
+    if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        return cuda_fail(cudaGetLastError(), "status reset");
     ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f};
     int nkeys = 0;
-    cudaError_t err = forward(K, codebook, f, wk.keys, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
+    cudaError_t err = forward(K, codebook, f, wk, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "forward");
+}
+
+int tcq_workspace_status(const void* ws, size_t ws_bytes, int64_t n_tiles, int K, void* stream) {
+    if (K < 2 || K > 4) return TCQ_E_BAD_K;
+    if (n_tiles <= 0) return n_tiles == 0 ? TCQ_OK : TCQ_E_BAD_COUNT;
+    int num_sms = 0;
+    int rc = current_num_sms(&num_sms);
+    if (rc != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(const_cast<void*>(ws), ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    unsigned int host = 0;
+    cudaError_t err = cudaMemcpyAsync(&host, wk.status, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return cuda_fail(err, "status read");
+    return host == 0 ? TCQ_OK : TCQ_E_DEVICE_TIMEOUT;
 }
 
 int64_t tcq_encode_launches(int64_t n_tiles, int K, size_t ws_bytes) {

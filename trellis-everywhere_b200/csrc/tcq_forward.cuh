@@ -255,8 +255,9 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
 // Implemented once per K in tcq_forward_k{2,3,4}.cu.
 // `keys` ([n][4] 64-bit scratch) enables the cluster kernel; *nkeys is then the number of
 // per-CTA partial minima written per tile (0: the single-CTA kernel ran and wrote e_final).
+// `status`: device word in which the cluster kernel sets bit 0 if one of its bounded waits gave up.
 template <int K>
-cudaError_t launch_forward(int codebook, const ForwardArgs& args, unsigned long long* keys, int num_sms,
-                           cudaStream_t stream, int* nkeys);
+cudaError_t launch_forward(int codebook, const ForwardArgs& args, unsigned long long* keys, unsigned int* status,
+                           int num_sms, cudaStream_t stream, int* nkeys);
 
 }  // namespace tcq

@@ -13,10 +13,16 @@
 //     (the owner of h' = (h * Q + l) mod HN), so each result is stored once, straight into the
 //     consumer's shared memory: a local store or a distributed-shared-memory store
 //     (cluster.map_shared_rank), never both;
-//   * steps are separated by the hardware cluster barrier.  The group's tiles are split into
-//     two sets that alternate; the phase that publishes one set's step is opened (arrive) in
-//     the middle of the other set's step and closed (wait) at its end, so neither the release
-//     fence nor the barrier latency is exposed;
+//   * the stores are asynchronous (st.async) and each one reports its 16 bytes to an mbarrier
+//     in the consumer CTA; a CTA starts a step when the mbarrier of its input buffer has
+//     counted the whole buffer.  No thread ever executes a memory fence, which matters because
+//     a release fence on this chip waits for every outstanding store of the SM, including the
+//     backpointer rows on their way to HBM;
+//   * the only other synchronisation is write-after-read: nobody may store into a buffer that
+//     a neighbour is still reading.  The hardware cluster barrier handles that with relaxed
+//     arrives at the end of every step and a wait just before the next step's first store;
+//   * the group's tiles form two sets that alternate, so both kinds of wait normally find
+//     their condition already true: the other set's step has run in between;
 //   * backpointers: each CTA packs the argmins of its slice into shared memory and streams
 //     the previous step's row slice to HBM with 128-bit stores, as the plain kernel does.
 //
@@ -40,17 +46,55 @@ constexpr size_t cluster_smem_bytes() {
     return size_t(2) * GS * 2 * (Geo<K>::E / C) * 4 + size_t(2) * 2 * GS * (Geo<K>::ROWB / C) + size_t(2) * GS * kT * 4 + 64 * 8;
 }
 
-// Split-phase hardware cluster barrier (all threads of all CTAs of the cluster take part).
-#ifdef TCQ_X_RELAXED
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
-#else
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-#endif
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Hardware cluster barrier, split phase, no memory ordering: used only to keep stores away from
+// buffers that are still being read.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_relaxed() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
+
+// ---- mbarrier + asynchronous distributed-shared-memory stores ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+// shared::cta address -> the same location in CTA `rank` of the cluster (shared::cluster address)
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// one arrival that also announces `bytes` of asynchronous stores for the phase in progress
+__device__ __forceinline__ void mbar_expect(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: gives up after kMbarSpins polls (each poll may itself sleep for a while in hardware);
+// the caller records the failure and carries on, so a counting bug shows up as an error status
+// and wrong codes, never as a hang.
+constexpr int kMbarSpins = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+    for (int i = 0; i < kMbarSpins; ++i)
+        if (mbar_try_wait(mbar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void st_async_v4(uint32_t dst, float x, float y, float z, float w, uint32_t mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(dst), "f"(x), "f"(y), "f"(z), "f"(w), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void st_async_v2(uint32_t dst, float x, float y, uint32_t mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+                 ::"r"(dst), "f"(x), "f"(y), "r"(mbar) : "memory");
+}
 
 struct ClusterArgs {
     ForwardArgs f;
     unsigned long long* keys;   // [n][C] out: per-CTA (metric bits << 32 | edge) minima of the final metrics, or nullptr
+    unsigned int* status;       // out: bit 0 is set if a bounded mbarrier wait ever gave up (results are then invalid)
 };
 
 template <int K, int CB, int C, int GS, int NT, int LU>
@@ -81,7 +125,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     float* const cost = reinterpret_cast<float*>(smem_raw);                          // [G][2][EC]
     unsigned char* const stage = smem_raw + size_t(G) * 2 * EC * 4;                   // [2][G][ROWBC]
     float* const wv = reinterpret_cast<float*>(stage + size_t(2) * G * ROWBC);        // [G][256]
-    unsigned long long* const red = reinterpret_cast<unsigned long long*>(wv + G * kT);
+    unsigned long long* const red = reinterpret_cast<unsigned long long*>(wv + G * kT);   // [32] reduction scratch
+    unsigned long long* const mbar = red + 32;     // [2 sets][2 buffers] mbarriers counting the bytes of each metric buffer
 
     const int tid = threadIdx.x;
     const bool constrained = a.overlap != nullptr;
@@ -93,7 +138,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // ---- this thread's items: codebook values and destinations, fixed for the whole launch ----
     int h_loc[NI];               // butterfly index inside this CTA
     int e_out[NI];               // first successor edge (global numbering)
-    float* dst[NI];              // where its LU results go: consumer CTA's metric buffer (tile 0, buffer 0)
+    uint32_t dst[NI];            // where its LU results go: shared::cluster address in the consumer CTA (tile 0, buffer 0)
+    uint32_t dst_bar[NI];        // the consumer CTA's mbarrier array (shared::cluster address)
     f32x2 cbv[NI][LU][Q / 2];    // codebook values of (q = 2j, 2j+1; successor lu)
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -105,12 +151,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         e_out[i] = e0;
         const int qn = e0 / HN, hn = e0 % HN;              // role of e0 in the next step: predecessor qn of butterfly hn
         const int owner = hn / HNC;
-        float* local = cost + qn * HNC + (hn % HNC);
-#ifdef TCQ_X_LOCAL
-        dst[i] = local;
-#else
-        dst[i] = owner == rank ? local : cluster.map_shared_rank(local, owner);
-#endif
+        dst[i] = map_to_rank(smem_u32(cost + qn * HNC + (hn % HNC)), owner);
+        dst_bar[i] = map_to_rank(smem_u32(mbar), owner);
         const uint32_t xb = uint32_t(e0) * MUL + ADD;
 #pragma unroll
         for (int lu = 0; lu < LU; ++lu)
@@ -129,9 +171,6 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // stream one step's row slices of tile set `s` (written during step t) to HBM (coalesced 128-bit stores)
     auto flush_set = [&](int s, int t, long long tile0) {
         if (t < t_store0) return;
-#ifdef TCQ_X_NOFLUSH
-        if (t >= 0) return;
-#endif
         const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(t & 1) * G * ROWBC + size_t(s) * GS * ROWBC);
         constexpr int V = ROWBC / 16;
         for (int i = tid; i < GS * V; i += NT) {
@@ -144,10 +183,28 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         }
     };
 
-    // one add-compare-select step of tile set `s` (tiles s*GS .. s*GS+GS-1), reading buffer `cur`
-    // (`arrive_mid`: half way through, open the pending barrier phase and then stream the set's
-    // previous rows to HBM; see the main loop)
-    auto step_set = [&](int s, int t, int cur, bool arrive_mid) {
+    constexpr uint32_t kBufBytes = uint32_t(GS) * EC * 4;     // bytes every (set, buffer) receives per step
+    uint32_t parity = 0;          // bit (2*s + b): parity of the phase the next wait on mbarrier (s, b) is for
+    bool timed_out = false;
+    bool wait_pending = false;    // the barrier phase entered during the PREVIOUS step_set has not been closed yet
+    auto war_wait = [&]() {
+        if (wait_pending) {
+            cluster_wait_relaxed();
+            wait_pending = false;
+        }
+    };
+
+    auto wait_buffer = [&](int s, int b) {        // all bytes of buffer b of set s have landed (then re-arm it)
+        const uint32_t m = smem_u32(mbar + (2 * s + b));
+        if (!mbar_wait(m, (parity >> (2 * s + b)) & 1u)) timed_out = true;
+        parity ^= 1u << (2 * s + b);
+        if (tid == 0) mbar_expect(m, kBufBytes);
+    };
+
+    // One add-compare-select step of tile set `s` (tiles s*GS .. s*GS+GS-1), reading buffer `cur`.
+    // Half way through, the set's previous backpointer rows are streamed to HBM.
+    auto step_set = [&](int s, int t, int cur) {
+        if (t > 0) wait_buffer(s, cur);
         f32x2 w2[GS];
 #pragma unroll
         for (int gg = 0; gg < GS; ++gg) {
@@ -157,64 +214,82 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         unsigned char* const st = stage + size_t(t & 1) * G * ROWBC;
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
-            f32x2 cin2[GS][Q / 2];
 #pragma unroll
             for (int gg = 0; gg < GS; ++gg) {
+                // The codebook is in registers, so tiles need not share anything: one tile at a time
+                // keeps only Q predecessor metrics live and lets the next tile's loads fly under
+                // this tile's arithmetic.
+                f32x2 cin2[Q / 2];
                 const float* cin = cost + (size_t(s * GS + gg) * 2 + cur) * EC + h_loc[i];
 #pragma unroll
-                for (int j = 0; j < Q / 2; ++j) cin2[gg][j] = pack2(cin[(2 * j) * HNC], cin[(2 * j + 1) * HNC]);
-            }
-            float outv[GS][LU];
-            float tags[GS];
+                for (int j = 0; j < Q / 2; ++j) cin2[j] = pack2(cin[(2 * j) * HNC], cin[(2 * j + 1) * HNC]);
+                constexpr int SV = LU < 4 ? LU : 4;            // successors per store (float2 or float4)
+                float outv[SV];
+                float tags = 0.0f;
+                const uint32_t d0 = dst[i] + uint32_t((size_t(s * GS + gg) * 2 + (cur ^ 1)) * EC * 4);
+                const uint32_t m = dst_bar[i] + uint32_t(2 * s + (cur ^ 1)) * 8u;
 #pragma unroll
-            for (int gg = 0; gg < GS; ++gg) tags[gg] = 0.0f;
-#pragma unroll
-            for (int lu = 0; lu < LU; ++lu) {
-                if (i == NI / 2 && lu == (NI > 1 ? 0 : LU / 2) && arrive_mid) {
-                    cluster_arrive();
-                    if (t > 0) flush_set(s, t - 1, tile0);
-                }
-#pragma unroll
-                for (int gg = 0; gg < GS; ++gg) {
+                for (int lu = 0; lu < LU; ++lu) {
+                    if (i == NI / 2 && gg == GS / 2 && lu == ((NI > 1 || GS > 1) ? 0 : LU / 2) && t > 0) flush_set(s, t - 1, tile0);
                     float c[Q];
 #pragma unroll
                     for (int j = 0; j < Q / 2; ++j)
-                        unpack2(cand_cost2(w2[gg], cbv[i][lu][j], cin2[gg][j], one2), c[2 * j], c[2 * j + 1]);
+                        unpack2(cand_cost2(w2[gg], cbv[i][lu][j], cin2[j], one2), c[2 * j], c[2 * j + 1]);
                     const float best = min_of<Q>(c);
                     float tag = float((Q - 1) << (lu * K));
 #pragma unroll
                     for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced(q, tag, c[q], best, zero, float(q << (lu * K)));
-                    outv[gg][lu] = best;
-                    tags[gg] = __fadd_rn(tags[gg], tag);
-                }
-            }
-#pragma unroll
-            for (int gg = 0; gg < GS; ++gg) {
-                float* d = dst[i] + (size_t(s * GS + gg) * 2 + (cur ^ 1)) * EC;
-                if constexpr (LU == 2) {
-                    *reinterpret_cast<float2*>(d) = make_float2(outv[gg][0], outv[gg][1]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < LU / 4; ++j)
-                        reinterpret_cast<float4*>(d)[j] = make_float4(outv[gg][4 * j], outv[gg][4 * j + 1], outv[gg][4 * j + 2], outv[gg][4 * j + 3]);
+                    outv[lu % SV] = best;
+                    tags = __fadd_rn(tags, tag);
+                    if (i == NI - 1 && gg == GS - 1 && lu == 0) {
+                        // Every input of this step has been loaded AND used (the first successor of the
+                        // last tile of the last item consumed all of its predecessors' metrics), so this
+                        // thread no longer reads the input buffers: tell the cluster, well before anyone
+                        // needs to know.  (The barrier's phases are sequential: close the previous one first.)
+                        war_wait();
+                        cluster_arrive_relaxed();
+                    }
+                    if (lu % SV == SV - 1) {
+                        // Results leave as soon as a store's worth is ready (fewer live registers).
+                        // Write-after-read: the buffer written now was read by every CTA one step of this
+                        // set ago; the barrier phase that every thread entered during the previous
+                        // step_set (of the other set) proves it, and it is closed before the first store.
+                        war_wait();
+                        const uint32_t d = d0 + uint32_t(lu + 1 - SV) * 4u;
+                        if constexpr (SV == 2) st_async_v2(d, outv[0], outv[1], m);
+                        else st_async_v4(d, outv[0], outv[1], outv[2], outv[3], m);
+                    }
                 }
                 unsigned char* sb = st + (s * GS + gg) * ROWBC + ((e_out[i] - rank * EC) * K) / 8;
                 if constexpr (PAIRED) {
                     // lanes 2m (chunk 0) and 2m+1 (chunk 1) hold the two halves of one butterfly's bits
-                    const float other = __shfl_xor_sync(0xffffffffu, tags[gg], 1);
+                    const float other = __shfl_xor_sync(0xffffffffu, tags, 1);
                     if ((tid & 1) == 0) {
-                        const uint32_t bits = __float2uint_rz(tags[gg]) | (__float2uint_rz(other) << ITEM_BITS);
+                        const uint32_t bits = __float2uint_rz(tags) | (__float2uint_rz(other) << ITEM_BITS);
 #pragma unroll
                         for (int b = 0; b < 2 * ITEM_BITS / 8; ++b) sb[b] = (unsigned char)(bits >> (8 * b));
                     }
                 } else {
-                    const uint32_t bits = __float2uint_rz(tags[gg]);
+                    const uint32_t bits = __float2uint_rz(tags);
 #pragma unroll
                     for (int b = 0; b < ITEM_BITS / 8; ++b) sb[b] = (unsigned char)(bits >> (8 * b));
                 }
             }
         }
+        wait_pending = true;          // the phase entered above is closed during the next step_set
     };
+
+    // ---- mbarriers: one arrival (the re-arming thread) plus kBufBytes of stores per phase ----
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(mbar + i), 1);
+        mbar_fence_init();
+    }
+    cluster.sync();                      // every CTA's mbarriers exist before anyone can signal them
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mbar_expect(smem_u32(mbar + i), kBufBytes);
+    }
 
     for (long long grp = cluster_id; grp < ngroups; grp += nclusters) {
         tile0 = grp * G;
@@ -236,25 +311,17 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         }
         cluster.sync();   // every CTA's buffers are initialised before anyone stores into them
 
-        // Two tile sets alternate, and the barrier phase that publishes one set's step is opened
-        // (arrive) HALF WAY THROUGH the other set's next step and closed (wait) at its end:
-        //   * the arrive carries release semantics, i.e. it waits for this thread's earlier
-        //     stores (remote shared memory, backpointer rows) to be performed.  The rows of the
-        //     set's previous step are therefore streamed to HBM right AFTER the arrive, a whole
-        //     step before the next one, so that no fence ever finds them in flight;
-        //   * the second half of the step covers the barrier's own latency.
-        // Staging rows of set s, step t-1 are read in the middle of its step t: after the phase
-        // that published them closed, and before the arrive (middle of the other set's next step)
-        // of the phase that lets step t+1 overwrite them.
-        step_set(0, 0, 0, false);
+        // The two tile sets alternate; every step_set waits for its input buffer's bytes, computes,
+        // waits for the previous step_set's barrier phase before its first store, stores, arrives.
+        step_set(0, 0, 0);
         for (int t = 0; t < kT; ++t) {
-            const int cur = t & 1;
-            step_set(1, t, cur, true);       // middle: arrive for "set 0, step t", then stream set 1's step t-1
-            cluster_wait();                  // set 0, step t: complete in every CTA
-            if (t + 1 < kT) step_set(0, t + 1, cur ^ 1, true);   // middle: arrive for "set 1, step t", stream set 0's step t
-            else { cluster_arrive(); }
-            cluster_wait();                  // set 1, step t: complete in every CTA
+            step_set(1, t, t & 1);
+            if (t + 1 < kT) step_set(0, t + 1, (t + 1) & 1);
         }
+        cluster_wait_relaxed();          // closes the phase opened by the last step_set
+        wait_pending = false;
+        wait_buffer(0, 0);               // step 255 wrote the final metrics into buffer 0
+        wait_buffer(1, 0);
         flush_set(0, kT - 1, tile0);
         flush_set(1, kT - 1, tile0);
 
@@ -299,6 +366,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         }
         cluster.sync();   // nobody may start re-initialising while a neighbour still reads or is written to
     }
+    if (timed_out && ca.status != nullptr) atomicOr(ca.status, 1u);
 }
 
 }  // namespace tcq

@@ -25,7 +25,7 @@ static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_
 // Cluster form.  Returns cudaErrorNotSupported (and launches nothing) if this device cannot
 // co-schedule a cluster of C CTAs with the kernel's shared-memory footprint.
 template <int K, int CB, int C, int GS, int NT, int LU>
-static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, cudaStream_t stream) {
+static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, unsigned int* status, cudaStream_t stream) {
     auto kern = tcq_forward_cluster_kernel<K, CB, C, GS, NT, LU>;
     constexpr size_t smem = cluster_smem_bytes<K, C, GS>();
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -58,7 +58,7 @@ static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long lo
     const long long ngroups = (a.n + G - 1) / G;
     const long long ncl = ngroups < maxc ? ngroups : maxc;
     cfg.gridDim = dim3(unsigned(ncl * C));
-    ClusterArgs ca{a, keys};
+    ClusterArgs ca{a, keys, status};
     return cudaLaunchKernelEx(&cfg, kern, ca);
 }
 
@@ -69,19 +69,17 @@ static inline int pick_cluster_set(long long n, int num_sms, int C) {
     return (n + 3) / 4 >= clusters ? 2 : 1;
 }
 
-// Which step kernel runs for a launch of n tiles.  Returns the cluster size (2 or 4) or 0 for
-// the single-CTA kernel.  Default: 2-CTA clusters once there is a full round of 4-tile groups
-// for every cluster (always for K = 2, where the single-CTA kernel can hold only one tile per
-// SM and so shares no codebook work); below that the single-CTA kernel's smaller groups finish
-// a small batch sooner.  TCQ_FORWARD_KERNEL = cta | cluster2 | cluster4 overrides (comparison runs).
-static inline int cluster_size_choice(long long n, int num_sms, bool always_cluster) {
+// Which step kernel runs.  Returns the cluster size (2 or 4) or 0 for the single-CTA kernel.
+// Default: 2-CTA clusters (all 148 SMs of a B200 pair up; clusters of 4 leave 16 SMs idle).
+// TCQ_FORWARD_KERNEL = cta | cluster2 | cluster4 overrides it for comparison runs; the single-CTA
+// kernel is also the fallback on a device that cannot co-schedule clusters.
+static inline int cluster_size_choice() {
     const char* v = std::getenv("TCQ_FORWARD_KERNEL");
     if (v != nullptr) {
         if (std::strcmp(v, "cta") == 0) return 0;
-        if (std::strcmp(v, "cluster2") == 0) return 2;
         if (std::strcmp(v, "cluster4") == 0) return 4;
     }
-    return (always_cluster || n >= 4LL * (num_sms / 2)) ? 2 : 0;
+    return 2;
 }
 
 // Relative time of one group of G tiles: G tiles of add-compare-select work plus

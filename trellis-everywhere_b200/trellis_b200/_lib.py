@@ -28,6 +28,7 @@ SIGNATURES = {
     "tcq_encode_tb_static": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]),
     "tcq_viterbi_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
     "tcq_forward_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _int, _vp, _sz, _vp]),
+    "tcq_workspace_status": (_int, [_vp, _sz, _i64, _int, _vp]),
     "tcq_encode_launches": (_i64, [_i64, _int, _sz]),
     "tcq_decode_packed": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
     "tcq_decode_symbols": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),
@@ -78,6 +79,6 @@ def check(code: int, what: str) -> None:
     msg = L.tcq_strerror(code).decode()
     if code == -7:
         raise TcqError(f"{what}: {msg}: {L.tcq_last_cuda_error().decode()}")
-    if code == -6:
+    if code in (-6, -10):
         raise TcqError(f"{what}: {msg}")
     raise ValueError(f"{what}: {msg}")
