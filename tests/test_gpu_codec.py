@@ -231,3 +231,25 @@ def test_matrix_quantizer_end_to_end(q):
     assert wq.shape == w.shape and rel < 0.12
     with pytest.raises(ValueError):
         q.tcq_quantize_weight(w, K=2, lut="mcg", backend="triton")
+
+
+def test_workspace_status_and_bounded_wait_selftest(q):
+    """A healthy encode leaves status 0; the self-test, which makes the step kernel's waits impossible to
+    satisfy, must come back (no hang), report a device timeout, and leave the library usable."""
+    L = q._lib.lib()
+    torch.manual_seed(7)
+    w = torch.randn(8, 256, device="cuda")
+    ws = torch.empty(int(L.tcq_workspace_bytes(8, 3)), dtype=torch.uint8, device="cuda")
+    packed = torch.empty(8, 24, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.tcq_encode_tb(w.data_ptr(), 8, 3, 2, packed.data_ptr(), None, None, None, ws.data_ptr(), ws.numel(), s) == 0
+    assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == 0
+    rc = L.tcq_selftest_wait_timeout(w.data_ptr(), 8, 3, ws.data_ptr(), ws.numel(), s)
+    if rc == -8:
+        pytest.skip("single-CTA step kernel in use: no bounded waits to exercise")
+    assert rc == 0
+    assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == -10          # TCQ_E_DEVICE_TIMEOUT
+    again = torch.empty_like(packed)
+    assert L.tcq_encode_tb(w.data_ptr(), 8, 3, 2, again.data_ptr(), None, None, None, ws.data_ptr(), ws.numel(), s) == 0
+    assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == 0
+    assert torch.equal(again, packed)

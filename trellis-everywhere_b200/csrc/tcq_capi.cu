@@ -173,14 +173,14 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
         cudaError_t err;
         // pass 1: tile rotated by half its length, free start; only the second half of the
         // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
-        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f};
+        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f, 0};
         int nkeys = 0;
         if ((err = forward(K, codebook, f1, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
         TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, nkeys ? wk.keys : nullptr, nkeys, wk.overlap,
                          nullptr, nullptr, nullptr, nullptr};
         if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
         // pass 2: true order, start and end tied to the overlap (qtip.py:142)
-        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f};
+        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f, 0};
         if ((err = forward(K, codebook, f2, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
         TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, 0, nullptr, nullptr,
                          bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
@@ -209,7 +209,7 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
         cudaError_t err;
         ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
-                      overlap ? nullptr : wk.e_final, nullptr, 1.0f};
+                      overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0};
         int nkeys = 0;
         if ((err = forward(K, codebook, f, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
         const bool use_keys = overlap == nullptr && nkeys > 0;
@@ -235,7 +235,7 @@ int tcq_forward_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess)
         return cuda_fail(cudaGetLastError(), "status reset");
-    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f};
+    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0};
     int nkeys = 0;
     cudaError_t err = forward(K, codebook, f, wk, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "forward");
@@ -254,6 +254,27 @@ int tcq_workspace_status(const void* ws, size_t ws_bytes, int64_t n_tiles, int K
     if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess) return cuda_fail(err, "status read");
     return host == 0 ? TCQ_OK : TCQ_E_DEVICE_TIMEOUT;
+}
+
+int tcq_selftest_wait_timeout(const float* w, int64_t n_tiles, int K, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_common(K, 0, n_tiles);
+    if (rc != TCQ_OK) return rc;
+    if (n_tiles < 1 || n_tiles > 8) return TCQ_E_BAD_COUNT;
+    if (w == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(w, 16)) return TCQ_E_MISALIGNED;
+    int num_sms = 0;
+    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
+    if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
+    // every metric buffer is told to expect 16 bytes more than the cluster will ever send
+    ForwardArgs f{w, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16};
+    int nkeys = 0;
+    cudaError_t err = forward(K, kCbMcg, f, wk, num_sms, s, &nkeys);
+    if (err != cudaSuccess) return cuda_fail(err, "forward (self-test)");
+    return nkeys > 0 ? TCQ_OK : TCQ_E_BAD_ARGUMENT;   // the single-CTA kernel has no bounded waits to test
 }
 
 int64_t tcq_encode_launches(int64_t n_tiles, int K, size_t ws_bytes) {

@@ -47,7 +47,8 @@ struct ForwardArgs {
     unsigned char* bp;       // [n][bp_steps][E*K/8] packed backpointers
     int* e_final;            // [n] out: argmin edge of the final metrics (lowest index on ties), or nullptr
     float* final_cost;       // [n] out: final metric at overlap[tile] (constrained) / its minimum, or nullptr
-    float one;               // must be 1.0f: run-time multiplier of the predicated-FMUL conditional move
+    float one;               // must be 1.0f: run-time constant of the fused arithmetic tricks (see tcq_common.cuh)
+    int inject_extra_bytes;  // 0; the wait self-test sets 16 so that the cluster kernel's byte counts can never be met
 };
 
 template <int K, int G>

@@ -29,6 +29,7 @@ SIGNATURES = {
     "tcq_viterbi_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
     "tcq_forward_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _int, _vp, _sz, _vp]),
     "tcq_workspace_status": (_int, [_vp, _sz, _i64, _int, _vp]),
+    "tcq_selftest_wait_timeout": (_int, [_vp, _i64, _int, _vp, _sz, _vp]),
     "tcq_encode_launches": (_i64, [_i64, _int, _sz]),
     "tcq_decode_packed": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
     "tcq_decode_symbols": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),
