@@ -253,3 +253,20 @@ def test_workspace_status_and_bounded_wait_selftest(q):
     assert L.tcq_encode_tb(w.data_ptr(), 8, 3, 2, again.data_ptr(), None, None, None, ws.data_ptr(), ws.numel(), s) == 0
     assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == 0
     assert torch.equal(again, packed)
+
+
+@pytest.mark.parametrize("K,name", [(2, "mcg"), (3, "3inst"), (4, "1mad")])
+def test_repeated_encodes_are_deterministic(q, K, name):
+    """The step kernel's CTAs exchange data through shared memory of neighbouring SMs; a missing ordering
+    would show up as run-to-run differences.  Same input, many launches, several group shapes."""
+    g = torch.Generator(device="cuda").manual_seed(11 * K)
+    for n in (6, 7, 150, 601):
+        w = torch.randn(n, 256, generator=g, device="cuda")
+        first = q.encode(w, K, name, want_bits=True)
+        for _ in range(6):
+            again = q.encode(w, K, name, want_bits=True)
+            assert torch.equal(again.packed, first.packed) and torch.equal(again.sse, first.sse)
+            assert torch.equal(again.dq, first.dq)
+        states = q.viterbi_pass_b200(w, K, None, name, roll=128)
+        for _ in range(4):
+            assert torch.equal(q.viterbi_pass_b200(torch.roll(w, 128, dims=1), K, None, name), states)
