@@ -147,10 +147,9 @@ TCQ_API int tcq_workspace_status(const void *ws, size_t ws_bytes, int64_t n_tile
 
 /*
  * Self-test of the bounded waits: runs one pass of the step kernel on 1..8 tiles while telling
- * every metric buffer to expect 16 bytes more than will ever arrive.  Each thread's first wait then
- * runs out after its poll limit (a few tenths of a second), later waits poll once, the kernel
- * finishes normally with garbage results, and tcq_workspace_status afterwards must report
- * TCQ_E_DEVICE_TIMEOUT.  Nothing faults, traps or spins without limit.  Returns TCQ_E_BAD_ARGUMENT
+ * the buffers of the final path metrics to expect 16 bytes more than will ever arrive.  The last
+ * wait of every thread then runs out after its time limit (about a quarter of a second), the kernel
+ * finishes normally, and tcq_workspace_status afterwards must report TCQ_E_DEVICE_TIMEOUT.  Nothing faults, traps or spins without limit.  Returns TCQ_E_BAD_ARGUMENT
  * if the device runs the single-CTA step kernel (which has no such waits).  No reference counterpart.
  */
 TCQ_API int tcq_selftest_wait_timeout(const float *w, int64_t n_tiles, int K, void *ws, size_t ws_bytes, void *stream);

@@ -269,7 +269,7 @@ int tcq_selftest_wait_timeout(const float* w, int64_t n_tiles, int K, void* ws, 
     if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
-    // every metric buffer is told to expect 16 bytes more than the cluster will ever send
+    // the buffers of the final metrics are told to expect 16 bytes more than the cluster will ever send
     ForwardArgs f{w, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16};
     int nkeys = 0;
     cudaError_t err = forward(K, kCbMcg, f, wk, num_sms, s, &nkeys);
