@@ -189,6 +189,34 @@ def test_quality_on_gaussian(q):
     assert mse[2] > mse[3] > mse[4]
 
 
+def test_first_configuration_reproduces_reference_distortion(q, oracle, luts):
+    """Configuration 1 of the benchmark list: torch.manual_seed(0) Gaussian tiles, 1MAD, K = 2, 256 tiles.
+    The reference's own encoder gives MSE 0.068643 on it (measured when the goldens were made)."""
+    torch.manual_seed(0)
+    w = torch.randn(256, 256)
+    r = q.encode(w.cuda(), 2, "1mad", want_bits=True)
+    mse = float(r.sse.double().sum() / w.numel())
+    assert abs(mse - 0.068643) < 2e-6
+    bits, dq = oracle.viterbi_tb(w[:12].numpy(), 2, luts["1mad"])
+    assert np.array_equal(_np(r.bits[:12]), bits) and same_bits(_np(r.dq[:12]), dq)
+
+
+def test_rate_distortion_table(q):
+    """Configuration 4: K = 2, 3, 4 x three codebooks on 4096 Gaussian tiles.  Bounds bracket the reference's
+    published figures for 64 tiles of the same generator (K2 0.069-0.075, K3 0.0181-0.0188, K4 0.0047-0.0049)."""
+    torch.manual_seed(0)
+    w = torch.randn(4096, 256).cuda()
+    lo = {2: 0.066, 3: 0.0170, 4: 0.0044}
+    hi = {2: 0.078, 3: 0.0200, 4: 0.0053}
+    for name in CODEBOOKS:
+        prev = 1.0
+        for K in KS:
+            mse = float(q.encode(w, K, name).sse.double().sum() / w.numel())
+            assert lo[K] < mse < hi[K], (name, K, mse)
+            assert mse < prev
+            prev = mse
+
+
 def test_host_tensors_round_trip_through_pinned_memory(q):
     torch.manual_seed(3)
     w = torch.randn(9, 256)
@@ -196,6 +224,28 @@ def test_host_tensors_round_trip_through_pinned_memory(q):
     r_gpu = q.encode(w.cuda(), 3, "3inst", want_bits=True)
     assert not r_cpu.packed.is_cuda and not r_cpu.dq.is_cuda
     assert torch.equal(r_cpu.packed, r_gpu.packed.cpu()) and torch.equal(r_cpu.dq, r_gpu.dq.cpu())
+
+
+def test_host_encode_pipeline_over_many_chunks(q, monkeypatch):
+    """Host tensors are streamed through the GPU in chunks on three overlapping streams; ragged last chunk,
+    more chunks than staging buffers, caller-provided pinned outputs."""
+    monkeypatch.setattr(q, "_HOST_CHUNK", 5)
+    torch.manual_seed(8)
+    w = torch.randn(23, 256)
+    ref = q.encode(w.cuda(), 3, "mcg", want_bits=True)
+    out = q.Encoded(torch.empty(23, 24, dtype=torch.int32, pin_memory=True), torch.empty(23, 256, pin_memory=True),
+                    torch.empty(23, pin_memory=True), torch.empty(23, 256, dtype=torch.int64, pin_memory=True))
+    for _ in range(3):
+        r = q.encode(w, 3, "mcg", want_bits=True, out=out)
+        assert r.packed is out.packed and r.dq is out.dq
+        assert torch.equal(r.packed, ref.packed.cpu()) and torch.equal(r.dq, ref.dq.cpu())
+        assert torch.equal(r.sse, ref.sse.cpu()) and torch.equal(r.bits, ref.bits.cpu())
+    fresh = q.encode(w, 3, "mcg")
+    assert fresh.packed.is_pinned() and torch.equal(fresh.packed, ref.packed.cpu()) and fresh.bits is None
+    with pytest.raises(ValueError):
+        q.encode(w, 3, "mcg", out=q.Encoded(torch.empty(3, 24, dtype=torch.int32), None, None, None))
+    with pytest.raises(ValueError):
+        q.encode(w.cuda(), 3, "mcg", out=out)
 
 
 def test_encoding_a_reconstruction_is_lossless(q, golden):

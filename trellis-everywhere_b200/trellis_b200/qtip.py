@@ -149,13 +149,111 @@ class Encoded(NamedTuple):
     bits: Optional[torch.Tensor]         # int64 [n, 256] symbols
 
 
+def _encode_device(wd: torch.Tensor, K: int, cid: int, packed, dq, sse, bits) -> None:
+    """One C-ABI call on device tensors (outputs preallocated; None = not wanted).  No host sync."""
+    n = wd.shape[0]
+    if not n:
+        return
+    dev = wd.device
+    ws = _workspace(dev, n, K)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tcq_encode_tb(wd.data_ptr(), n, K, cid, packed.data_ptr(),
+                                      bits.data_ptr() if bits is not None else None,
+                                      dq.data_ptr() if dq is not None else None,
+                                      sse.data_ptr() if sse is not None else None,
+                                      ws.data_ptr(), ws.numel(), _stream(dev))
+    _lib.check(rc, "tcq_encode_tb")
+
+
+_HOST_CHUNK = 2 * 3552          # tiles per pipelined chunk of a host-tensor encode (two workspace chunks)
+_copy_streams: dict = {}
+
+
+def _encode_host(w: torch.Tensor, K: int, cid: int, dev: torch.device, want_dq: bool, want_sse: bool, want_bits: bool,
+                 out: Optional["Encoded"]) -> "Encoded":
+    """Encode host tiles: chunks are copied in, encoded and copied out on three streams that overlap.
+
+    The copy of chunk i+1 to the device and the copy of chunk i-1's results to the host run under the
+    encode of chunk i, so the PCIe traffic costs one chunk of latency, not a pass over the data.
+    Results land in pinned host tensors (``out`` if given, else freshly allocated); the call returns
+    after the last copy has finished.
+    """
+    n = w.shape[0]
+    nw = T_SEQ * K // 32
+    wh = w.to(torch.float32).contiguous()
+    if not wh.is_pinned():
+        wh = wh.pin_memory()
+
+    def host(shape, dtype, given):
+        if given is not None:
+            if tuple(given.shape) != tuple(shape) or given.dtype != dtype or given.is_cuda:
+                raise ValueError("`out` tensors must be host tensors of the result's shape and dtype")
+            return given
+        return torch.empty(shape, dtype=dtype, pin_memory=True)
+
+    h_packed = host((n, nw), torch.int32, out.packed if out else None)
+    h_dq = host((n, T_SEQ), torch.float32, out.dq if out else None) if want_dq else None
+    h_sse = host((n,), torch.float32, out.sse if out else None) if want_sse else None
+    h_bits = host((n, T_SEQ), torch.int64, out.bits if out else None) if want_bits else None
+    if n == 0:
+        return Encoded(h_packed, h_dq, h_sse, h_bits)
+
+    key = dev.index
+    if key not in _copy_streams:
+        _copy_streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    s_in, s_out = _copy_streams[key]
+    main = torch.cuda.current_stream(dev)
+    c = min(n, _HOST_CHUNK)
+    d_w = [torch.empty((c, T_SEQ), dtype=torch.float32, device=dev) for _ in range(2)]
+    d_packed = [torch.empty((c, nw), dtype=torch.int32, device=dev) for _ in range(2)]
+    d_dq = [torch.empty((c, T_SEQ), dtype=torch.float32, device=dev) if want_dq else None for _ in range(2)]
+    d_sse = [torch.empty((c,), dtype=torch.float32, device=dev) if want_sse else None for _ in range(2)]
+    d_bits = [torch.empty((c, T_SEQ), dtype=torch.int64, device=dev) if want_bits else None for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    s_in.wait_stream(main)
+    starts = list(range(0, n, c))
+    for i, lo in enumerate(starts):
+        b, m = i & 1, min(c, n - lo)
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_done[b])            # the encode that read this input buffer has finished
+            d_w[b][:m].copy_(wh[lo:lo + m], non_blocking=True)
+            ev_in[b].record(s_in)
+        main.wait_event(ev_in[b])
+        if i >= 2:
+            main.wait_event(ev_out[b])                 # this buffer's previous results are on the host
+        _encode_device(d_w[b][:m], K, cid, d_packed[b][:m], d_dq[b][:m] if want_dq else None,
+                       d_sse[b][:m] if want_sse else None, d_bits[b][:m] if want_bits else None)
+        ev_done[b].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[b])
+            h_packed[lo:lo + m].copy_(d_packed[b][:m], non_blocking=True)
+            if want_dq:
+                h_dq[lo:lo + m].copy_(d_dq[b][:m], non_blocking=True)
+            if want_sse:
+                h_sse[lo:lo + m].copy_(d_sse[b][:m], non_blocking=True)
+            if want_bits:
+                h_bits[lo:lo + m].copy_(d_bits[b][:m], non_blocking=True)
+            ev_out[b].record(s_out)
+    for t in d_w + d_packed + d_dq + d_sse + d_bits:      # keep the staging buffers alive on the side streams
+        if t is not None:
+            t.record_stream(s_in)
+            t.record_stream(s_out)
+    s_out.synchronize()                                   # the caller reads host memory next
+    return Encoded(h_packed, h_dq, h_sse, h_bits)
+
+
 @torch.no_grad()
 def encode(w: torch.Tensor, K: int, codebook: CodebookLike, *, want_dq: bool = True, want_sse: bool = True,
-           want_bits: bool = False) -> Encoded:
-    """Tail-biting trellis encode of ``w [n, 256]`` (one C-ABI call, no host sync).
+           want_bits: bool = False, out: Optional[Encoded] = None) -> Encoded:
+    """Tail-biting trellis encode of ``w [n, 256]``.
 
-    Outputs live on the device of ``w`` (host tensors are staged through pinned
-    memory and the results copied back).
+    Device tensors: one C-ABI call, nothing synchronises, outputs on the same device.
+    Host tensors: the tiles are streamed through the GPU in chunks (copy in, encode, copy out
+    overlap) and the results come back as pinned host tensors; pass pinned tiles and preallocated
+    pinned ``out`` tensors (an ``Encoded`` with the wanted fields) to avoid per-call pinning.
     """
     if w.dim() != 2 or w.shape[1] != T_SEQ:
         raise ValueError(f"expected tiles of shape [n, {T_SEQ}], got {tuple(w.shape)}")
@@ -164,22 +262,16 @@ def encode(w: torch.Tensor, K: int, codebook: CodebookLike, *, want_dq: bool = T
     cid = codebook_id(codebook)
     dev = _cuda_device(w)
     n = w.shape[0]
+    if not w.is_cuda:
+        return _encode_host(w, K, cid, dev, want_dq, want_sse, want_bits, out)
+    if out is not None:
+        raise ValueError("`out` is for host-tensor encodes; device results are allocated by the call")
     wd = _to_dev(w, dev, torch.float32)
     packed = torch.empty((n, T_SEQ * K // 32), dtype=torch.int32, device=dev)
     dq = torch.empty((n, T_SEQ), dtype=torch.float32, device=dev) if want_dq else None
     sse = torch.empty((n,), dtype=torch.float32, device=dev) if want_sse else None
     bits = torch.empty((n, T_SEQ), dtype=torch.int64, device=dev) if want_bits else None
-    if n:
-        ws = _workspace(dev, n, K)
-        with torch.cuda.device(dev):
-            rc = _lib.lib().tcq_encode_tb(wd.data_ptr(), n, K, cid, packed.data_ptr(),
-                                          bits.data_ptr() if want_bits else None,
-                                          dq.data_ptr() if want_dq else None,
-                                          sse.data_ptr() if want_sse else None,
-                                          ws.data_ptr(), ws.numel(), _stream(dev))
-        _lib.check(rc, "tcq_encode_tb")
-    if not w.is_cuda:
-        packed, dq, sse, bits = (None if x is None else x.cpu() for x in (packed, dq, sse, bits))
+    _encode_device(wd, K, cid, packed, dq, sse, bits)
     return Encoded(packed, dq, sse, bits)
 
 
