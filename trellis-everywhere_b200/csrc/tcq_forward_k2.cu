@@ -15,13 +15,12 @@ cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, unsigned i
     *nkeys = 0;
     const int csize = cluster_size_choice();
     if (keys != nullptr && csize != 0) {
-        const bool two_sets = pick_cluster_set(a.n, num_sms, csize) == 2;
         cudaError_t err;
         if (csize == 2)
-            err = launch_cluster_variant<2, CB, 2, 1, kNT, kCLU2>(a, keys, status, stream);   // two sets of two tiles do not fit 227 KiB
+            err = launch_cluster_variant<2, CB, 2, 1, kNT, kCLU2>(a, keys, status, stream);   // larger sets do not fit 227 KiB
         else
-            err = two_sets ? launch_cluster_variant<2, CB, 4, 2, kNT, kCLU4>(a, keys, status, stream)
-                           : launch_cluster_variant<2, CB, 4, 1, kNT, kCLU4>(a, keys, status, stream);
+            err = pick_cluster_set(a.n, num_sms, 4, 2) == 2 ? launch_cluster_variant<2, CB, 4, 2, kNT, kCLU4>(a, keys, status, stream)
+                                                           : launch_cluster_variant<2, CB, 4, 1, kNT, kCLU4>(a, keys, status, stream);
         if (err != cudaErrorNotSupported) {
             *nkeys = csize;
             return err;

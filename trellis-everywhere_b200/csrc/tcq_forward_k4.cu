@@ -15,14 +15,17 @@ cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, unsigned i
     *nkeys = 0;
     const int csize = cluster_size_choice();
     if (keys != nullptr && csize != 0) {
-        const bool two_sets = pick_cluster_set(a.n, num_sms, csize) == 2;
         cudaError_t err;
-        if (csize == 2)
-            err = two_sets ? launch_cluster_variant<4, CB, 2, 2, kNT, kCLU2>(a, keys, status, stream)
-                           : launch_cluster_variant<4, CB, 2, 1, kNT, kCLU2>(a, keys, status, stream);
-        else
-            err = two_sets ? launch_cluster_variant<4, CB, 4, 2, kNT, kCLU4>(a, keys, status, stream)
-                           : launch_cluster_variant<4, CB, 4, 1, kNT, kCLU4>(a, keys, status, stream);
+        if (csize == 2) {
+            switch (pick_cluster_set(a.n, num_sms, 2, 3)) {
+                case 1: err = launch_cluster_variant<4, CB, 2, 1, kNT, kCLU2>(a, keys, status, stream); break;
+                case 2: err = launch_cluster_variant<4, CB, 2, 2, kNT, kCLU2>(a, keys, status, stream); break;
+                default: err = launch_cluster_variant<4, CB, 2, 3, kNT, kCLU2>(a, keys, status, stream); break;
+            }
+        } else {
+            err = pick_cluster_set(a.n, num_sms, 4, 2) == 2 ? launch_cluster_variant<4, CB, 4, 2, kNT, kCLU4>(a, keys, status, stream)
+                                                           : launch_cluster_variant<4, CB, 4, 1, kNT, kCLU4>(a, keys, status, stream);
+        }
         if (err != cudaErrorNotSupported) {
             *nkeys = csize;
             return err;

@@ -62,11 +62,19 @@ static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long lo
     return cudaLaunchKernelEx(&cfg, kern, ca);
 }
 
-// Tile sets of one tile (2 tiles per cluster) finish a small batch sooner when there are
-// fewer groups of 4 than clusters; otherwise sets of two amortise the per-step overheads.
-static inline int pick_cluster_set(long long n, int num_sms, int C) {
+// Tiles per set (a cluster advances two sets): the size that finishes n tiles soonest on the
+// device's clusters, counting whole rounds of groups and a small fixed cost per step and group.
+static inline int pick_cluster_set(long long n, int num_sms, int C, int gs_max) {
     const long long clusters = num_sms / C > 0 ? num_sms / C : 1;
-    return (n + 3) / 4 >= clusters ? 2 : 1;
+    int best = 1;
+    double best_t = 1e300;
+    for (int gs = 1; gs <= gs_max; ++gs) {
+        const long long groups = (n + 2 * gs - 1) / (2 * gs);
+        const long long rounds = (groups + clusters - 1) / clusters;
+        const double t = double(rounds) * (2.0 * gs + 0.15);
+        if (t < best_t - 1e-9) { best_t = t; best = gs; }
+    }
+    return best;
 }
 
 // Which step kernel runs.  Returns the cluster size (2 or 4) or 0 for the single-CTA kernel.
