@@ -52,6 +52,7 @@ extern "C" {
 #define TCQ_E_WORKSPACE (-6)     /* workspace smaller than tcq_workspace_min_bytes() */
 #define TCQ_E_CUDA (-7)          /* CUDA runtime error (no device, launch failure) */
 #define TCQ_E_BAD_ARGUMENT (-8)  /* other invalid argument (roll, T, ...) */
+#define TCQ_E_NONFINITE_INPUT (-11) /* tcq_workspace_status: a weight of the last call was NaN or infinite */
 #define TCQ_E_DEVICE_TIMEOUT (-10) /* a bounded in-kernel wait gave up (tcq_workspace_status) */
 #define TCQ_E_TOO_MANY_TILES (-9) /* batch larger than tcq_encode_tb_static_max_tiles(K) */
 
@@ -140,8 +141,10 @@ TCQ_API int tcq_forward_pass(const float *w, int64_t n_tiles, int K, int codeboo
  * this workspace with the same n_tiles and K.  The step kernel's CTAs exchange path metrics
  * through shared memory of neighbouring SMs and wait for them with a bounded number of polls;
  * a wait that runs out sets a flag in the workspace instead of hanging.  This call copies the
- * flag to the host and SYNCHRONISES the stream (the only entry point that does): TCQ_OK, or
- * TCQ_E_DEVICE_TIMEOUT if the outputs of that call must not be used.  No reference counterpart.
+ * flag to the host and SYNCHRONISES the stream (the only entry point that does): TCQ_OK,
+ * TCQ_E_DEVICE_TIMEOUT if the outputs of that call must not be used, or TCQ_E_NONFINITE_INPUT if
+ * some weight was NaN or infinite (the kernels never trap on such input; they encode it to
+ * meaningless codes and flag it here).  No reference counterpart.
  */
 TCQ_API int tcq_workspace_status(const void *ws, size_t ws_bytes, int64_t n_tiles, int K, void *stream);
 

@@ -320,3 +320,22 @@ def test_repeated_encodes_are_deterministic(q, K, name):
         states = q.viterbi_pass_b200(w, K, None, name, roll=128)
         for _ in range(4):
             assert torch.equal(q.viterbi_pass_b200(torch.roll(w, 128, dims=1), K, None, name), states)
+
+
+def test_non_finite_weights_are_flagged_not_trapped(q):
+    torch.manual_seed(9)
+    w = torch.randn(10, 256, device="cuda")
+    ref = q.encode(w, 3, "mcg").packed
+    q.workspace_status(10, 3)                                  # healthy
+    bad = w.clone()
+    bad[4, 17] = float("nan")
+    bad[7, 200] = float("inf")
+    r = q.encode(bad, 3, "mcg", want_bits=True)
+    torch.cuda.synchronize()                                    # the kernels ran to completion
+    assert int(r.bits.min()) >= 0 and int(r.bits.max()) < 8     # codes stay well-formed
+    good = [i for i in range(10) if i not in (4, 7)]
+    assert torch.equal(r.packed[good], ref[good])               # other tiles are unaffected
+    with pytest.raises(q._lib.TcqError, match="NaN or infinite"):
+        q.workspace_status(10, 3)
+    q.encode(w, 3, "mcg")
+    q.workspace_status(10, 3)                                  # the flag is per call

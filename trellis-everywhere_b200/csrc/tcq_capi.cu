@@ -90,9 +90,9 @@ int carve(void* ws, size_t ws_bytes, long long n, int K, int num_sms, Workspace*
 
 cudaError_t forward(int K, int codebook, const ForwardArgs& a, const Workspace& wk, int num_sms, cudaStream_t s, int* nkeys) {
     switch (K) {
-        case 2: return launch_forward<2>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
-        case 3: return launch_forward<3>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
-        case 4: return launch_forward<4>(codebook, a, wk.keys, wk.status, num_sms, s, nkeys);
+        case 2: return launch_forward<2>(codebook, a, wk.keys, num_sms, s, nkeys);
+        case 3: return launch_forward<3>(codebook, a, wk.keys, num_sms, s, nkeys);
+        case 4: return launch_forward<4>(codebook, a, wk.keys, num_sms, s, nkeys);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -123,6 +123,7 @@ const char* tcq_strerror(int code) {
         case TCQ_E_WORKSPACE: return "workspace is smaller than tcq_workspace_min_bytes(K)";
         case TCQ_E_CUDA: return "CUDA runtime error (see tcq_last_cuda_error)";
         case TCQ_E_BAD_ARGUMENT: return "invalid argument";
+        case TCQ_E_NONFINITE_INPUT: return "a weight was NaN or infinite; the codes of its tile are meaningless";
         case TCQ_E_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up; the outputs of that call are invalid";
         case TCQ_E_TOO_MANY_TILES: return "more tiles than the static scratch holds (see tcq_encode_tb_static_max_tiles)";
         default: return "unknown error code";
@@ -173,14 +174,14 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
         cudaError_t err;
         // pass 1: tile rotated by half its length, free start; only the second half of the
         // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
-        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f, 0};
+        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f, 0, wk.status};
         int nkeys = 0;
         if ((err = forward(K, codebook, f1, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
         TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, nkeys ? wk.keys : nullptr, nkeys, wk.overlap,
                          nullptr, nullptr, nullptr, nullptr};
         if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
         // pass 2: true order, start and end tied to the overlap (qtip.py:142)
-        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f, 0};
+        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f, 0, wk.status};
         if ((err = forward(K, codebook, f2, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
         TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, 0, nullptr, nullptr,
                          bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
@@ -209,7 +210,7 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
         cudaError_t err;
         ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
-                      overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0};
+                      overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0, wk.status};
         int nkeys = 0;
         if ((err = forward(K, codebook, f, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
         const bool use_keys = overlap == nullptr && nkeys > 0;
@@ -235,7 +236,7 @@ int tcq_forward_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess)
         return cuda_fail(cudaGetLastError(), "status reset");
-    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0};
+    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0, wk.status};
     int nkeys = 0;
     cudaError_t err = forward(K, codebook, f, wk, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "forward");
@@ -253,7 +254,8 @@ int tcq_workspace_status(const void* ws, size_t ws_bytes, int64_t n_tiles, int K
     cudaError_t err = cudaMemcpyAsync(&host, wk.status, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
     if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess) return cuda_fail(err, "status read");
-    return host == 0 ? TCQ_OK : TCQ_E_DEVICE_TIMEOUT;
+    if (host & 1u) return TCQ_E_DEVICE_TIMEOUT;
+    return (host & 2u) ? TCQ_E_NONFINITE_INPUT : TCQ_OK;
 }
 
 int tcq_selftest_wait_timeout(const float* w, int64_t n_tiles, int K, void* ws, size_t ws_bytes, void* stream) {
@@ -270,7 +272,7 @@ int tcq_selftest_wait_timeout(const float* w, int64_t n_tiles, int K, void* ws, 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
     // the buffers of the final metrics are told to expect 16 bytes more than the cluster will ever send
-    ForwardArgs f{w, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16};
+    ForwardArgs f{w, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16, wk.status};
     int nkeys = 0;
     cudaError_t err = forward(K, kCbMcg, f, wk, num_sms, s, &nkeys);
     if (err != cudaSuccess) return cuda_fail(err, "forward (self-test)");

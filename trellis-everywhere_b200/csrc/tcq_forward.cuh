@@ -49,6 +49,7 @@ struct ForwardArgs {
     float* final_cost;       // [n] out: final metric at overlap[tile] (constrained) / its minimum, or nullptr
     float one;               // must be 1.0f: run-time constant of the fused arithmetic tricks (see tcq_common.cuh)
     int inject_extra_bytes;  // 0; the wait self-test sets 16 so that the cluster kernel's byte counts can never be met
+    unsigned int* status;    // device word or nullptr: bit 0 = a bounded wait gave up, bit 1 = a weight was NaN or infinite
 };
 
 template <int K, int G>
@@ -88,7 +89,9 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
         // ---- load the group's weights, initialise the metrics (qtip.py:161-165) ----
         for (int i = tid; i < G * kT; i += NT) {
             const long long tile = tile0 + (i >> 8);
-            wv[i] = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
+            const float x = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
+            wv[i] = x;
+            if (!isfinite(x) && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
         }
         {
             const float init = constrained ? kInf : 0.0f;
@@ -256,9 +259,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
 // Implemented once per K in tcq_forward_k{2,3,4}.cu.
 // `keys` ([n][4] 64-bit scratch) enables the cluster kernel; *nkeys is then the number of
 // per-CTA partial minima written per tile (0: the single-CTA kernel ran and wrote e_final).
-// `status`: device word in which the cluster kernel sets bit 0 if one of its bounded waits gave up.
 template <int K>
-cudaError_t launch_forward(int codebook, const ForwardArgs& args, unsigned long long* keys, unsigned int* status,
-                           int num_sms, cudaStream_t stream, int* nkeys);
+cudaError_t launch_forward(int codebook, const ForwardArgs& args, unsigned long long* keys, int num_sms,
+                           cudaStream_t stream, int* nkeys);
 
 }  // namespace tcq

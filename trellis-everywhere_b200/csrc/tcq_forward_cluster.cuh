@@ -99,7 +99,6 @@ __device__ __forceinline__ void st_async_v2(uint32_t dst, float x, float y, uint
 struct ClusterArgs {
     ForwardArgs f;
     unsigned long long* keys;   // [n][C] out: per-CTA (metric bits << 32 | edge) minima of the final metrics, or nullptr
-    unsigned int* status;       // out: bit 0 is set if a bounded mbarrier wait ever gave up (results are then invalid)
 };
 
 template <int K, int CB, int C, int GS, int NT, int LU>
@@ -309,7 +308,9 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         // ---- weights and initial metrics (src/trellis/qtip.py:161-165) ----
         for (int i = tid; i < G * kT; i += NT) {
             const long long tile = tile0 + (i >> 8);
-            wv[i] = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
+            const float x = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
+            wv[i] = x;
+            if (!isfinite(x) && rank == 0 && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
         }
         {
             const float init = constrained ? kInf : 0.0f;
@@ -382,7 +383,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         }
         cluster.sync();   // nobody may start re-initialising while a neighbour still reads or is written to
     }
-    if (timed_out && ca.status != nullptr) atomicOr(ca.status, 1u);
+    if (timed_out && a.status != nullptr) atomicOr(a.status, 1u);
 }
 
 }  // namespace tcq

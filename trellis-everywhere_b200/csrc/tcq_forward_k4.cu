@@ -11,20 +11,20 @@ constexpr int kCLU4 = 2;     // successors per work item with 4 CTAs per cluster
 constexpr int kCLU2 = 4;     // ... with 2 CTAs per cluster (64 codebook values per thread)
 
 template <int CB>
-cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, unsigned int* status, int num_sms, cudaStream_t stream, int* nkeys) {
+cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t stream, int* nkeys) {
     *nkeys = 0;
     const int csize = cluster_size_choice();
     if (keys != nullptr && csize != 0) {
         cudaError_t err;
         if (csize == 2) {
             switch (pick_cluster_set(a.n, num_sms, 2, 3)) {
-                case 1: err = launch_cluster_variant<4, CB, 2, 1, kNT, kCLU2>(a, keys, status, stream); break;
-                case 2: err = launch_cluster_variant<4, CB, 2, 2, kNT, kCLU2>(a, keys, status, stream); break;
-                default: err = launch_cluster_variant<4, CB, 2, 3, kNT, kCLU2>(a, keys, status, stream); break;
+                case 1: err = launch_cluster_variant<4, CB, 2, 1, kNT, kCLU2>(a, keys, stream); break;
+                case 2: err = launch_cluster_variant<4, CB, 2, 2, kNT, kCLU2>(a, keys, stream); break;
+                default: err = launch_cluster_variant<4, CB, 2, 3, kNT, kCLU2>(a, keys, stream); break;
             }
         } else {
-            err = pick_cluster_set(a.n, num_sms, 4, 2) == 2 ? launch_cluster_variant<4, CB, 4, 2, kNT, kCLU4>(a, keys, status, stream)
-                                                           : launch_cluster_variant<4, CB, 4, 1, kNT, kCLU4>(a, keys, status, stream);
+            err = pick_cluster_set(a.n, num_sms, 4, 2) == 2 ? launch_cluster_variant<4, CB, 4, 2, kNT, kCLU4>(a, keys, stream)
+                                                           : launch_cluster_variant<4, CB, 4, 1, kNT, kCLU4>(a, keys, stream);
         }
         if (err != cudaErrorNotSupported) {
             *nkeys = csize;
@@ -41,12 +41,12 @@ cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, unsigned i
 }  // namespace
 
 template <>
-cudaError_t launch_forward<4>(int codebook, const ForwardArgs& a, unsigned long long* keys, unsigned int* status,
-                               int num_sms, cudaStream_t stream, int* nkeys) {
+cudaError_t launch_forward<4>(int codebook, const ForwardArgs& a, unsigned long long* keys, int num_sms,
+                               cudaStream_t stream, int* nkeys) {
     switch (codebook) {
-        case kCb1Mad:  return launch_cb<kCb1Mad>(a, keys, status, num_sms, stream, nkeys);
-        case kCb3Inst: return launch_cb<kCb3Inst>(a, keys, status, num_sms, stream, nkeys);
-        case kCbMcg:   return launch_cb<kCbMcg>(a, keys, status, num_sms, stream, nkeys);
+        case kCb1Mad:  return launch_cb<kCb1Mad>(a, keys, num_sms, stream, nkeys);
+        case kCb3Inst: return launch_cb<kCb3Inst>(a, keys, num_sms, stream, nkeys);
+        case kCbMcg:   return launch_cb<kCbMcg>(a, keys, num_sms, stream, nkeys);
         default:       return cudaErrorInvalidValue;
     }
 }

@@ -25,7 +25,7 @@ static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_
 // Cluster form.  Returns cudaErrorNotSupported (and launches nothing) if this device cannot
 // co-schedule a cluster of C CTAs with the kernel's shared-memory footprint.
 template <int K, int CB, int C, int GS, int NT, int LU>
-static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, unsigned int* status, cudaStream_t stream) {
+static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, cudaStream_t stream) {
     auto kern = tcq_forward_cluster_kernel<K, CB, C, GS, NT, LU>;
     constexpr size_t smem = cluster_smem_bytes<K, C, GS>();
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -58,7 +58,7 @@ static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long lo
     const long long ngroups = (a.n + G - 1) / G;
     const long long ncl = ngroups < maxc ? ngroups : maxc;
     cfg.gridDim = dim3(unsigned(ncl * C));
-    ClusterArgs ca{a, keys, status};
+    ClusterArgs ca{a, keys};
     return cudaLaunchKernelEx(&cfg, kern, ca);
 }
 

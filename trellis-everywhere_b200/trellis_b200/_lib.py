@@ -80,6 +80,6 @@ def check(code: int, what: str) -> None:
     msg = L.tcq_strerror(code).decode()
     if code == -7:
         raise TcqError(f"{what}: {msg}: {L.tcq_last_cuda_error().decode()}")
-    if code in (-6, -10):
+    if code in (-6, -10, -11):
         raise TcqError(f"{what}: {msg}")
     raise ValueError(f"{what}: {msg}")

@@ -78,6 +78,19 @@ def _workspace(dev: torch.device, n_tiles: int, K: int) -> torch.Tensor:
     return ws
 
 
+def workspace_status(n_tiles: int, K: int, device=None) -> None:
+    """Health of the last device encode of ``n_tiles`` tiles at ``K`` on the current stream (synchronises).
+
+    Raises ``TcqError`` if a bounded in-kernel wait gave up (outputs invalid) or if some weight of
+    that call was NaN or infinite (its tile's codes are meaningless); returns None otherwise.
+    """
+    dev = torch.device(device) if device is not None else _cuda_device()
+    ws = _workspace(dev, n_tiles, K)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tcq_workspace_status(ws.data_ptr(), ws.numel(), n_tiles, K, _stream(dev))
+    _lib.check(rc, "tcq_workspace_status")
+
+
 def release_workspaces() -> None:
     """Free the cached scratch buffers."""
     _workspaces.clear()
