@@ -278,7 +278,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         bp_bytes = chunk * (128 + 256) / 2 * (1 << (16 - K_BITS)) * K_BITS / 8      # mean of the two passes
         ck = clocks.summary()
         roofline = {
-            "bound": "alu", "kernel": "Viterbi step kernel (tcq_forward_cluster_kernel<K=3, 3INST, 2 CTAs>)",
+            "bound": "alu", "kernel": "Viterbi step kernel (tcq_forward_cluster_kernel<K=3, 3INST, 2 CTAs per cluster, 6 tiles per group>)",
             "achieved": achieved / 1e12, "peak": peak_lane_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_lane_ops,
             "peak_source": f"{sms} SMs x 128 fp32/int lanes x {sm_max_mhz:.0f} MHz (max SM clock of MEASURED_PEAKS.json"
                            f"{'' if peaks else '; file absent, nominal clock used'}); the path does no tensor-core or "
@@ -286,9 +286,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "algorithmic": "4 lane-ops (fsub, fmul, fadd, compare-select) x 65536 state evaluations per tile-step",
             "launch_ms": {"pass1": kern_ms[0], "pass2": kern_ms[1]}, "tiles_per_launch": chunk,
             "frac_at_sampled_clock": (achieved / (sms * 128 * ck["sm_mhz"] * 1e6)) if ck.get("sm_mhz") else None,
-            # ncu dram__bytes_read+write of a 592-tile launch pair = 0.831 of its algorithmic backpointer bytes
-            # (profiles/step_kernel_k3_3inst_592tiles_ncu_full.md), scaled here by the tiles per launch
-            "traffic": 0.831 * bp_bytes,
+            # ncu dram__bytes_read+write of an 888-tile launch pair = 0.89 of its algorithmic backpointer bytes
+            # (profiles/step_kernel_k3_3inst_888tiles_ncu_full.md), scaled here by the tiles per launch
+            "traffic": 0.89 * bp_bytes,
             "hbm": {"algorithmic_bytes_per_launch": bp_bytes, "achieved_GBps": bp_bytes / (avg_kernel_ms * 1e-3) / 1e9,
                     "peak_GBps": peaks.get("hbm_gbs"), "note": "packed backpointer stream, K bits per edge per step"},
         }
