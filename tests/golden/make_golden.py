@@ -20,6 +20,7 @@ Files written (all small, committed):
                   (3INST, K=3), the second benchmark configuration in miniature
   decode.npz      decode_recursive / decode_window on random symbols (with and
                   without a start state), pack_bits_np words, wrapped decode
+  quant.npz       tcq_quantize_weight (incoherence processing + plain TCQ, fp32 DP) on a small matrix
   ldlq.npz        teacher-forced LDLQ: the compensated row blocks the reference's
                   ``enc`` closure received and the reconstructions it returned
 """
@@ -116,6 +117,16 @@ def main(ref_root: str) -> None:
         tb = enc[f"mcg_K{K}_bits"].astype(np.int64)
         dec[f"K{K}_packed"] = pack_bits_np(tb, K)
     np.savez_compressed(os.path.join(HERE, "decode.npz"), **dec)
+
+    # ---- matrix quantizer end to end (plain) ----
+    from trellis.qtip import tcq_quantize_weight
+    torch.manual_seed(4)
+    wq_in = torch.randn(128, 256) * 0.02
+    qd = {"w": wq_in.numpy()}
+    for K in (2, 3):
+        qd[f"mcg_K{K}_w_hat"] = tcq_quantize_weight(wq_in, K=K, lut=luts["mcg"], seed=0, tile_batch=256,
+                                                    dp_dtype=torch.float32, backend="torch").numpy()
+    np.savez_compressed(os.path.join(HERE, "quant.npz"), **qd)
 
     # ---- LDLQ, teacher forced ----------------------------------------------------------
     torch.manual_seed(1)

@@ -272,6 +272,22 @@ def test_full_size_properties(q):
     assert torch.equal(idem.dq, r.dq[:2048]) and float(idem.sse.max()) == 0.0
 
 
+@pytest.mark.parametrize("K", [2, 3])
+def test_matrix_quantizer_against_reference_result(q, golden, K):
+    """tcq_quantize_weight end to end against the reference's own W_hat (fp32 DP, CPU).  The incoherence
+    processing runs in PyTorch on the GPU here and on the CPU there, so the tiles differ in the last ulp and a
+    few codes may flip (each flip is smeared over a 128 x 128 block by the inverse Hadamard); tolerance:
+    quantisation error of the two results within 1 % of each other, and their difference below 1e-3 of the
+    result's energy (a handful of flipped codes out of 32 768 gives about 3e-5)."""
+    g = golden["quant"]
+    w = torch.from_numpy(g["w"]).cuda()
+    ref = torch.from_numpy(g[f"mcg_K{K}_w_hat"]).cuda()
+    ours = q.tcq_quantize_weight(w, K=K, lut="mcg", seed=0)
+    rel = lambda x: float(((w - x) ** 2).mean() / w.square().mean())
+    assert abs(rel(ours) - rel(ref)) / rel(ref) < 0.01
+    assert float(((ours - ref) ** 2).sum() / ref.square().sum()) < 1e-3
+
+
 def test_matrix_quantizer_end_to_end(q):
     # tests/test_qtip.py:95-105: relative MSE of a 2-bit layer stays below 0.12
     torch.manual_seed(4)
