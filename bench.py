@@ -278,7 +278,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         bp_bytes = chunk * (128 + 256) / 2 * (1 << (16 - K_BITS)) * K_BITS / 8      # mean of the two passes
         ck = clocks.summary()
         roofline = {
-            "bound": "alu", "kernel": "Viterbi step kernel (tcq_forward_cluster_kernel<K=3, 3INST, 2 CTAs per cluster, 6 tiles per group>)",
+            "bound": "alu", "kernel": f"Viterbi step kernel (tcq_forward_cluster_kernel, K={K_BITS}, {CODEBOOK}, 2 CTAs per cluster)",
             "achieved": achieved / 1e12, "peak": peak_lane_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_lane_ops,
             "peak_source": f"{sms} SMs x 128 fp32/int lanes x {sm_max_mhz:.0f} MHz (max SM clock of MEASURED_PEAKS.json"
                            f"{'' if peaks else '; file absent, nominal clock used'}); the path does no tensor-core or "
@@ -301,10 +301,11 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             cpu = {"value": rate, "unit": "weights/s", "cores": threads, "kind": "port",
                    "sample": f"first {n_s} tiles of the same workload, {dt:.1f} s"}
         line = {
-            "metric": "weights encoded/sec (L=16, K=3)", "value": total_weights / (ms * 1e-3), "unit": "weights/s",
+            "metric": f"weights encoded/sec (L=16, K={K_BITS})", "value": total_weights / (ms * 1e-3), "unit": "weights/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD if not args.tiles else f"REDUCED to {n} tiles (profiling case) of: " + WORKLOAD,
+            "config": {"workload": (WORKLOAD if not args.tiles else f"REDUCED to {n} tiles (profiling case) of: " + WORKLOAD)
+                       + ("" if (K_BITS, CODEBOOK) == (3, "3inst") else f" -- SIDE MEASUREMENT at K={K_BITS}, {CODEBOOK}"),
                        "K": K_BITS, "codebook": CODEBOOK, "tiles_per_gpu": n,
                        "parallelism": f"{world} x whole matrices, NCCL all-gather of packed codes" if world > 1 else "1 GPU",
                        "l2": "each step streams 2.7 GiB of backpointer scratch, far more than the 126 MB L2, so nothing "
@@ -330,10 +331,16 @@ def main() -> None:
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
     ap.add_argument("--ref-tiles", type=int, default=256, help="tiles per step of the reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--K", type=int, default=3, choices=(2, 3, 4),
+                    help="bits per weight; anything but the default 3 is a side measurement, not the benchmark")
+    ap.add_argument("--codebook", default="3inst", choices=("1mad", "3inst", "mcg"),
+                    help="codebook; anything but the default 3inst is a side measurement, not the benchmark")
     ap.add_argument("--tiles", type=int, default=0,
                     help="encode only the first N tiles of the workload (small cases for ncu captures; the printed line "
                          "is then not a benchmark result)")
     args = ap.parse_args()
+    global K_BITS, CODEBOOK
+    K_BITS, CODEBOOK = args.K, args.codebook
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
