@@ -23,6 +23,9 @@ Files written (all small, committed):
   quant.npz       tcq_quantize_weight (incoherence processing + plain TCQ, fp32 DP) on a small matrix
   ldlq.npz        teacher-forced LDLQ: the compensated row blocks the reference's
                   ``enc`` closure received and the reconstructions it returned
+  shard.npz       one packed-model shard written by the reference's own ``Shard`` / ``put_quant``
+                  (compiled from the exporter's syntax tree like ``pack_bits_np``): the .bin bytes,
+                  the .bin.json text and the inputs that went in.  ``... <checkout> shard`` makes only this file.
 """
 from __future__ import annotations
 
@@ -46,8 +49,55 @@ def _load_pack_bits_np(ref_root: str):
     return ns["pack_bits_np"]
 
 
-def main(ref_root: str) -> None:
+def _load_shard_writer(ref_root: str):
+    """The reference's Shard class and put_quant function, compiled alone from the exporter's syntax tree."""
+    import json
+    from trellis.qtip import _fit_block
+    path = os.path.join(ref_root, "scripts", "export_packed_8b.py")
+    tree = ast.parse(open(path).read(), filename=path)
+    want = [n for n in tree.body if (isinstance(n, ast.ClassDef) and n.name == "Shard")
+            or (isinstance(n, ast.FunctionDef) and n.name == "put_quant")]
+    ns = {"np": np, "os": os, "json": json, "_fit_block": _fit_block, "print": lambda *a, **k: None}
+    exec(compile(ast.Module(body=want, type_ignores=[]), path, "exec"), ns)
+    return ns["Shard"], ns["put_quant"]
+
+
+def make_shard(ref_root: str) -> None:
+    import tempfile
+    import zlib
+    from trellis.qtip import IPContext, T_SEQ, codebook_lut, viterbi_tb
+    Shard, put_quant = _load_shard_writer(ref_root)
+    pack_bits_np = _load_pack_bits_np(ref_root)
+    lut = codebook_lut("mcg")
+    torch.manual_seed(5)
+    n, k, K = 32, 64, 3
+    w = torch.randn(n, k) * 0.02
+    ip = IPContext(w, lut.square().mean().sqrt().item(), seed=zlib.crc32(b"x"))
+    tiles = ip.z.view(n // 16, 16, k // 16, 16).permute(0, 2, 1, 3).reshape(-1, T_SEQ)
+    bits, dq = viterbi_tb(tiles.contiguous(), K, lut, dp_dtype=torch.float32)
+    packed = pack_bits_np(bits.numpy().astype(np.int64), K)
+    w_hat = ip.restore(dq.view(n // 16, k // 16, 16, 16).permute(0, 2, 1, 3).reshape(n, k))
+    norm = torch.rand(k) + 0.5
+    name = "model.layers.0.self_attn.q_proj.weight"
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "layer_00.bin")
+        sh = Shard(path)
+        put_quant(sh, name, packed, ip, n, k, K)
+        sh.put("model.layers.0.input_layernorm.weight", norm.numpy(), np.float16)
+        sh.flush()
+        blob = np.fromfile(path, dtype=np.uint8)
+        index = open(path + ".json").read()
+    np.savez_compressed(os.path.join(HERE, "shard.npz"), w=w.numpy(), packed=packed, su=ip.su.numpy(), sv=ip.sv.numpy(),
+                        in_s=ip.in_s.numpy(), out_s=ip.out_s.numpy(), scale=np.float64(ip.scale), norm=norm.numpy(),
+                        w_hat=w_hat.numpy(), bin=blob, index=np.frombuffer(index.encode(), dtype=np.uint8),
+                        name=np.frombuffer(name.encode(), dtype=np.uint8), K=np.int64(K))
+
+
+def main(ref_root: str, only: str = "") -> None:
     sys.path.insert(0, os.path.join(ref_root, "src"))
+    if only == "shard":
+        make_shard(ref_root)
+        return
     import trellis.ldlq as ldlq_mod
     from trellis.qtip import (IPContext, T_SEQ, _viterbi_pass, codebook_lut, decode_recursive,
                               decode_window, viterbi_tb)
@@ -157,12 +207,13 @@ def main(ref_root: str) -> None:
         n_calls=np.int64(len(calls)),
         w=wm.numpy(), H=H.numpy().astype(np.float32), w_hat=what.numpy(),
     )
+    make_shard(ref_root)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) not in (2, 3):
         sys.exit(__doc__)
-    main(sys.argv[1])
+    main(*sys.argv[1:])

@@ -102,3 +102,62 @@ def test_model_level_encode_packs_in_reference_tile_order(mods, tmp_path):
     res2, gathered2 = model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, out_dir=str(tmp_path))
     assert all(r["skipped"] for r in res2.values())
     assert all(torch.equal(gathered2[n], gathered[n]) for n in shapes)
+
+
+def test_matrices_in_flight_on_several_streams_give_the_same_codes(mods):
+    """encode_model(streams=3) overlaps matrices on one GPU; every matrix's packed words equal the serial run's."""
+    from trellis_b200 import model
+    shapes = {f"model.layers.0.{m}": s for m, s in
+              [("self_attn.q_proj", (128, 256)), ("self_attn.k_proj", (32, 256)), ("mlp.gate_proj", (256, 128)),
+               ("mlp.up_proj", (256, 128)), ("mlp.down_proj", (128, 256))]}
+    hess = lambda name, k, dev: model.synthetic_hessian(name, k, dev, rows=512)
+    serial, g1 = model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, streams=1)
+    logs = []
+    overlapped, g3 = model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, streams=3, log=logs.append)
+    assert set(g1) == set(g3) == set(shapes) and len(logs) == len(shapes)
+    for name in shapes:
+        assert torch.equal(g1[name], g3[name]), name
+        assert serial[name]["rel_err"] == overlapped[name]["rel_err"]
+
+    def boom(name, shape, dev):
+        raise RuntimeError("weights unavailable: " + name)
+    with pytest.raises(RuntimeError, match="weights unavailable"):
+        model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, weight_fn=boom, streams=2)
+
+
+def test_shard_from_the_gpu_encoder_equals_the_reference_shard_and_evaluates(mods, golden, tmp_path):
+    """Plain-TCQ matrix -> shard: the bytes equal the shard the reference's exporter wrote for the same matrix, and
+    y = W_hat x evaluated from the shard alone (restore folded into x and y, web/packed.js:163-182) matches the
+    reference's W_hat up to the fp16 rounding of the stored scale vectors."""
+    import zlib
+    from trellis_b200 import model, shards
+    q, _ = mods
+    g = golden["shard"]
+    name = bytes(g["name"]).decode()
+    w = torch.from_numpy(g["w"]).cuda()
+    n, k = w.shape
+    K = int(g["K"])
+    packed, w_hat, _ = model.encode_matrix(w, K, "mcg", zlib.crc32(b"x"))
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32), g["packed"])
+    assert torch.allclose(w_hat.cpu(), torch.from_numpy(g["w_hat"]), rtol=1e-5, atol=1e-8)
+    lut = q.codebook_lut("mcg", "cuda")
+    ip = q.IPContext(w, lut.square().mean().sqrt().item(), seed=zlib.crc32(b"x"))
+    path = shards.write_layer_shard(str(tmp_path), 0, {name[:-len(".weight")]: (packed, ip, n, k, K)},
+                                    {"model.layers.0.input_layernorm.weight": g["norm"]})
+    assert path.endswith("layer_00.bin") and shards.shard_done(path)
+    blob = np.fromfile(path, dtype=np.uint8)
+    ref = g["bin"]
+    assert blob.size == ref.size
+    differing = np.flatnonzero(blob != ref)
+    # packed words are bit-exact; scale vectors are fp16 of fp32 values that may differ in the last fp32 bit between
+    # the CPU and the GPU matmul of the Hadamard step, so allow a handful of fp16 last-place differences there
+    assert differing.size <= 8 and (differing.size == 0 or differing.min() >= g["packed"].nbytes)
+
+    man = shards.merge_manifest(str(tmp_path))
+    rec = shards.read_quant(str(tmp_path), man, name)
+    x = torch.randn(k, 3, generator=torch.Generator().manual_seed(0))
+    y = shards.packed_linear(rec, x).cpu()
+    want = torch.from_numpy(g["w_hat"]) @ x
+    assert y.shape == (n, 3)
+    assert float((y - want).norm() / want.norm()) < 2e-3          # fp16 scale vectors
+    assert torch.allclose(shards.packed_linear(rec, x[:, 0]).cpu(), y[:, 0], rtol=1e-5, atol=1e-7)

@@ -3,6 +3,7 @@ validation, the host logic of LDLQ / incoherence processing, and the multi-rank 
 import ctypes
 import os
 import re
+import zlib
 
 import numpy as np
 import pytest
@@ -221,3 +222,56 @@ def test_model_code_gather_over_gloo(tmp_path):
     port = 31500 + os.getpid() % 2000
     mp.start_processes(_gloo_model_gather_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True, start_method="spawn")
     assert os.path.exists(os.path.join(tmp_path, "ok"))
+
+
+def test_shard_writer_reproduces_the_reference_shard_byte_for_byte(tmp_path, golden):
+    """A shard written here from the same packed words and incoherence-processing vectors is the reference
+    exporter's file: identical .bin bytes and identical .bin.json index (scripts/export_packed_8b.py:65-79,134-143)."""
+    import json
+    import types
+    from trellis_b200 import shards
+    g = golden["shard"]
+    name = bytes(g["name"]).decode()
+    n, k = g["w"].shape
+    K = int(g["K"])
+    ip = types.SimpleNamespace(su=torch.from_numpy(g["su"]), sv=torch.from_numpy(g["sv"]), in_s=torch.from_numpy(g["in_s"]),
+                               out_s=torch.from_numpy(g["out_s"]), scale=float(g["scale"]))
+    path = str(tmp_path / "layer_00.bin")
+    assert not shards.shard_done(path)
+    sh = shards.Shard(path)
+    sh.put_quant(name, torch.from_numpy(g["packed"].view(np.int32)), ip, n, k, K)     # int32 words, as the GPU returns them
+    sh.put("model.layers.0.input_layernorm.weight", g["norm"], np.float16)
+    with pytest.raises(KeyError):
+        sh.put(name + ".bits", g["packed"], np.uint32)
+    with pytest.raises(ValueError):
+        sh.put("bad", g["norm"], np.float64)
+    sh.flush()
+    assert shards.shard_done(path)
+    assert np.array_equal(np.fromfile(path, dtype=np.uint8), g["bin"])
+    assert json.load(open(path + ".json")) == json.loads(bytes(g["index"]).decode())
+
+    man = shards.merge_manifest(str(tmp_path))
+    assert json.load(open(tmp_path / "manifest.json")) == man
+    q = shards.read_quant(str(tmp_path), man, name)
+    assert q["n_out"] == n and q["k_in"] == k and q["K"] == K and q["tiles_in"] == k // 16 and q["block"] == 64
+    assert np.array_equal(q["bits"], g["packed"]) and q["bits"].dtype == np.uint32
+    assert np.array_equal(q["su"].astype(np.float32), g["su"]) and np.array_equal(q["osc"], g["out_s"].astype(np.float16))
+    assert np.array_equal(shards.read_tensor(str(tmp_path), man, "model.layers.0.input_layernorm.weight"), g["norm"].astype(np.float16))
+    with pytest.raises(KeyError):
+        shards.read_tensor(str(tmp_path), man, name)
+
+    # the mirror's incoherence processing gives the same vectors as the reference's (same generator, same recipe)
+    mine = qtip.IPContext(torch.from_numpy(g["w"]), _mcg_rms(), seed=zlib.crc32(b"x"))
+    assert torch.equal(mine.su, ip.su) and torch.equal(mine.sv, ip.sv)
+    assert torch.allclose(mine.in_s, ip.in_s, rtol=1e-5) and torch.allclose(mine.out_s, ip.out_s, rtol=1e-5)
+    assert abs(mine.scale - ip.scale) < 1e-5 * ip.scale
+
+
+def _mcg_rms() -> float:
+    """RMS of the MCG codebook, computed on the host from its definition (qtip.py:51-56)."""
+    s = np.arange(65536, dtype=np.uint64)
+    v = (s * np.uint64(0xCBAC1FED)) & np.uint64(0xFFFFFFFF)
+    r = ((v & np.uint64(0x8FFF8FFF)) ^ np.uint64(0x3B603B60)).astype(np.uint32)
+    hi = (r >> np.uint32(16)).astype(np.uint16).view(np.float16).astype(np.float32)
+    lo = (r & np.uint32(0xFFFF)).astype(np.uint16).view(np.float16).astype(np.float32)
+    return float(torch.from_numpy(hi + lo).square().mean().sqrt().item())

@@ -19,6 +19,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import threading
 import time
 import zlib
 from typing import Callable, Dict, Optional, Sequence, Tuple
@@ -30,6 +31,9 @@ import torch.distributed as dist
 from . import dist as tdist
 from . import ldlq as tldlq
 from . import qtip
+
+
+_linalg_lock = threading.Lock()
 
 
 def qwen3_8b_shapes(layers: int = 36, hidden: int = 4096, inter: int = 12288, q_heads: int = 32, kv_heads: int = 8,
@@ -92,7 +96,8 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
         packed, zq = r.packed, qtip.from_tiles(r.dq, n, k)
     else:
         Ht = tldlq._transform_H(H.float(), ip.su, block=qtip._pow2_block(k, 128))
-        Lm = tldlq.block_ldl(tldlq.regularize_H(Ht, sigma_reg), b=16)
+        with _linalg_lock:                 # torch's lazily initialised linalg backends must not be entered by two threads at once
+            Lm = tldlq.block_ldl(tldlq.regularize_H(Ht, sigma_reg), b=16)
         if Lm is None:
             Lm = torch.zeros(k, k, device=dev)
         store = torch.empty((n // 16, k // 16, nw), dtype=torch.int32, device=dev)
@@ -113,10 +118,11 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
 def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg", ldlq_filter: Callable[[str], bool] = is_mlp,
                  weight_fn: Callable = synthetic_weight, hessian_fn: Optional[Callable] = synthetic_hessian,
                  out_dir: Optional[str] = None, device=None, group=None, gather: bool = True,
-                 log: Optional[Callable[[dict], None]] = None):
+                 log: Optional[Callable[[dict], None]] = None, streams: int = 1):
     """Encode this rank's share of the model; returns (results of this rank, gathered packed words on rank 0).
 
     ``results``: name -> {"tiles", "seconds", "weights_per_s", "rel_err", "ldlq", "skipped"}.
+    ``streams`` > 1 keeps that many matrices in flight on this GPU (one host thread + CUDA stream each).
     Works without an initialised process group (single process = rank 0 of 1).
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -127,20 +133,21 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
     results, packed_out = {}, {}
     if out_dir:
         os.makedirs(out_dir, exist_ok=True)
-    for name in mine:
+
+    def one(name: str, stream) -> None:
         n_out, k_in = shapes[name]
         path = os.path.join(out_dir, name + ".bits.npy") if out_dir else None
         if path and os.path.exists(path):                       # resume: finished in an earlier run
             packed_out[name] = torch.from_numpy(np.load(path)).to(dev)
             results[name] = {"tiles": packed_out[name].shape[0], "skipped": True}
-            continue
+            return
         use_ldlq = name in ldlq_names
         w = weight_fn(name, (n_out, k_in), dev)
         H = hessian_fn(name, k_in, dev) if use_ldlq else None
-        torch.cuda.synchronize(dev)
+        stream.synchronize()
         t0 = time.perf_counter()
         packed, _, rel = encode_matrix(w, K, codebook, seed_of(name), H)
-        torch.cuda.synchronize(dev)
+        stream.synchronize()
         dt = time.perf_counter() - t0
         rec = {"name": name, "rank": rank, "gpu": dev.index, "tiles": packed.shape[0], "seconds": dt,
                "weights_per_s": n_out * k_in / dt, "rel_err": rel, "ldlq": use_ldlq, "skipped": False}
@@ -152,7 +159,45 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
             os.replace(tmp, path)
         if log:
             log(rec)
-        del w, H
+
+    if streams <= 1:
+        for name in mine:
+            one(name, torch.cuda.current_stream(dev))
+    else:
+        # Several matrices in flight, one host thread and one CUDA stream each.  An LDLQ recursion is a serial
+        # chain of encoder calls of n_out/16 tiles, which rarely fill the last round of SMs; kernels of another
+        # matrix's chain take the idle SMs.  Results do not depend on the interleaving: every matrix has its own
+        # stream, scratch and seed.  "seconds" of a matrix then overlaps with its neighbours'.
+        todo = list(mine)
+        lock = threading.Lock()
+        errors = []
+        caller = torch.cuda.current_stream(dev)
+
+        def worker() -> None:
+            with torch.cuda.device(dev):
+                s = torch.cuda.Stream(dev)
+                s.wait_stream(caller)
+                with torch.cuda.stream(s):
+                    while True:
+                        with lock:
+                            if not todo or errors:
+                                break
+                            name = todo.pop(0)
+                        try:
+                            one(name, s)
+                        except BaseException as e:      # surfaced by the caller below
+                            with lock:
+                                errors.append(e)
+                            break
+                s.synchronize()
+
+        threads = [threading.Thread(target=worker, name=f"encode-stream-{i}") for i in range(min(streams, max(1, len(todo))))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errors:
+            raise errors[0]
     gathered = None
     if gather:
         gathered = gather_model_codes(shapes, ldlq_names, packed_out, K, world, rank, dev, group)
@@ -200,6 +245,7 @@ def main(argv=None) -> None:
     ap.add_argument("--codebook", default="mcg")
     ap.add_argument("--no-ldlq", action="store_true", help="plain TCQ everywhere (the reference's Hessian-free mode)")
     ap.add_argument("--hessian-rows", type=int, default=8192)
+    ap.add_argument("--streams", type=int, default=3, help="matrices in flight per GPU (1 = one after another)")
     ap.add_argument("--out", default=None, help="folder for <name>.bits.npy files and per-rank JSONL logs (enables resume)")
     args = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -222,7 +268,8 @@ def main(argv=None) -> None:
     hess = None if args.no_ldlq else (lambda name, k, d: synthetic_hessian(name, k, d, rows=args.hessian_rows))
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
-    results, gathered = encode_model(shapes, args.K, args.codebook, hessian_fn=hess, out_dir=args.out, device=dev, log=log)
+    results, gathered = encode_model(shapes, args.K, args.codebook, hessian_fn=hess, out_dir=args.out, device=dev, log=log,
+                                     streams=args.streams)
     torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
@@ -230,7 +277,7 @@ def main(argv=None) -> None:
     if rank == 0:
         total = sum(a * b for a, b in shapes.values())
         print(json.dumps({"summary": True, "matrices": len(shapes), "weights": total, "seconds": dt, "weights_per_s": total / dt,
-                          "world": world, "gathered_matrices": len(gathered) if gathered is not None else 0}), flush=True)
+                          "world": world, "streams": args.streams, "gathered_matrices": len(gathered) if gathered is not None else 0}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
