@@ -322,6 +322,95 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps(line), flush=True)
 
 
+def run_decode_matvec(args) -> None:
+    """Side measurement of the consumer of the packed format: y = x Zq^T from packed codes (lm_head-shaped matrix).
+
+    One step = one product of the [n_out, k_in] code matrix (K bits per weight, random code words: every bit pattern is a
+    valid stream) with ``m`` right-hand sides.  The packed words (larger than L2) stay resident in HBM, as weights do when
+    serving; ``e2e`` copies x from pinned host memory and y back inside the timing.
+    """
+    import numpy as np
+    import torch
+    from trellis_b200 import _lib, qtip
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n_out, k_in, m = args.n_out, args.k_in, args.m
+    tiles = (n_out // 16) * (k_in // 16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (tiles, 8 * K_BITS), dtype=torch.int32, device=dev, generator=g)
+    x = torch.randn(m, k_in, device=dev, generator=g)
+    xh = x.cpu().pin_memory()
+    yh = torch.empty((m, n_out), dtype=torch.float32, pin_memory=True)
+    launches = (m + 3) // 4
+
+    def step_device():
+        return qtip.decode_matvec(packed, n_out, k_in, K_BITS, CODEBOOK, x)
+
+    def step_host():
+        yh.copy_(qtip.decode_matvec(packed, n_out, k_in, K_BITS, CODEBOOK, xh.to(dev, non_blocking=True)), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    with ClockSampler(0) as clocks:
+        ms = timed(step_device)
+        ms_host = timed(step_host)
+        t_end = time.time() + 1.0                       # keep the GPU busy long enough for a few clock samples
+        while time.time() < t_end:
+            step_device()
+        torch.cuda.synchronize()
+    weights = n_out * k_in
+    peaks = measured_peaks()
+    hbm = peaks.get("hbm_gbs")
+    packed_gbs = weights * K_BITS / 8 / (ms * 1e-3) / 1e9
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    ck = clocks.summary()
+    line = {
+        "metric": f"weights decoded and multiplied/sec (decode-matvec, L=16, K={K_BITS})", "value": weights / (ms * 1e-3),
+        "unit": "weights/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"SIDE MEASUREMENT (consumer of the packed format): [{n_out}, {k_in}] code matrix, K={K_BITS}, "
+                               f"{CODEBOOK}, {m} right-hand side(s); packed words {weights * K_BITS / 8 / 2 ** 20:.0f} MiB resident "
+                               "in HBM (larger than L2, no flush needed)", "n_out": n_out, "k_in": k_in, "m": m},
+        "e2e": {"value": weights / (ms_host * 1e-3), "unit": "weights/s", "h2d_bytes_per_step": m * k_in * 4,
+                "d2h_bytes_per_step": m * n_out * 4},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "kernel": f"tcq_decode_matvec_kernel<K={K_BITS}, {CODEBOOK}>", "achieved": packed_gbs,
+                     "peak": hbm if hbm else 6650.0, "unit": "GB/s", "frac": packed_gbs / (hbm if hbm else 6650.0),
+                     "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if hbm else "fallback 6.65 TB/s (of fallback)",
+                     "traffic": None,
+                     "note": "the kernel is bound by instruction issue, not HBM: see weights_per_clk_per_sm",
+                     "weights_per_clk_per_sm": weights / (ms * 1e-3) / sms / ((ck["sm_mhz"] or 1965.0) * 1e6)},
+        "clocks": ck,
+    }
+    if not args.no_cpu_baseline:
+        from oracle import oracle as O
+        O.build()
+        rows = min(n_out, 2048)                              # bounded sample: the first tile rows of the same matrix
+        pk = packed[: (rows // 16) * (k_in // 16)].cpu().numpy().view(np.uint32)
+        xn = x.cpu().numpy()
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < min(args.cpu_seconds, 10.0):
+            zq = O.decode_packed(pk, K_BITS, CODEBOOK).reshape(rows // 16, k_in // 16, 16, 16).transpose(0, 2, 1, 3).reshape(rows, k_in)
+            _ = xn @ zq.T
+            reps += 1
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": rows * k_in * reps / dt, "unit": "weights/s", "cores": O.max_threads(), "kind": "port",
+                                "sample": f"first {rows} rows of the same matrix, window decode (C oracle) + numpy product, {reps} repeats"}
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -335,6 +424,11 @@ def main() -> None:
                     help="bits per weight; anything but the default 3 is a side measurement, not the benchmark")
     ap.add_argument("--codebook", default="3inst", choices=("1mad", "3inst", "mcg"),
                     help="codebook; anything but the default 3inst is a side measurement, not the benchmark")
+    ap.add_argument("--path", choices=("encode", "decode_matvec"), default="encode",
+                    help="encode = the benchmark; decode_matvec = side measurement of the packed format's consumer kernel")
+    ap.add_argument("--n-out", type=int, default=151936, help="decode_matvec: output rows (default: lm_head of the model shape)")
+    ap.add_argument("--k-in", type=int, default=4096, help="decode_matvec: input columns")
+    ap.add_argument("--m", type=int, default=1, help="decode_matvec: right-hand sides")
     ap.add_argument("--tiles", type=int, default=0,
                     help="encode only the first N tiles of the workload (small cases for ncu captures; the printed line "
                          "is then not a benchmark result)")
@@ -344,7 +438,12 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
+    if args.path == "decode_matvec":
+        if args.impl != "b200" or args.gpus != 1:
+            raise SystemExit("--path decode_matvec is a one-GPU side measurement of this library")
+        if rank == 0:
+            run_decode_matvec(args)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         if world != args.gpus:

@@ -174,6 +174,20 @@ TCQ_API int64_t tcq_encode_launches(int64_t n_tiles, int K, size_t ws_bytes);
 TCQ_API int tcq_decode_packed(const uint32_t *packed, int64_t n_tiles, int K, int codebook, float *dq, void *stream);
 
 /*
+ * Matrix-vector products straight from packed codes: y[j][row] = sum_col Zq[row][col] * x[j][col],
+ * Zq[row][col] = codebook(window at bit (255-t)*K of tile (row/16)*(k_in/16) + col/16,
+ * t = (row%16)*16 + col%16), never materialised.  Replaces the DECODE_MATMUL shader
+ * (web/kernels.js:105-128), which does the same for one vector with one thread per
+ * output row; the incoherence-processing fold around it (web/packed.js:163-182)
+ * stays with the caller.  fp32 accumulation in a fixed order (reproducible run to run).
+ *   packed [n_out/16 * k_in/16, 8*K] u32;  n_out, k_in multiples of 16
+ *   x [m][ldx] fp32 right-hand sides, 16-byte aligned, ldx >= k_in and a multiple of 4
+ *   y [m][ldy] fp32 results, ldy >= n_out;  m >= 0 (decoded once per four right-hand sides)
+ */
+TCQ_API int tcq_decode_matvec(const uint32_t *packed, int64_t n_out, int64_t k_in, int K, int codebook, const float *x,
+                      int64_t ldx, int m, float *y, int64_t ldy, void *stream);
+
+/*
  * Decode unpacked symbol streams of any length T (no wrap): state_t is the last
  * 16 bits of s0 followed by symbols 0..t.  Replaces decode_recursive and
  * decode_window (src/trellis/qtip.py:70-110), which are equal by construction.

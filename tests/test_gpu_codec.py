@@ -163,6 +163,51 @@ def test_pack_and_packed_decode(q, golden, K):
     assert same_bits(_np(q.decode_packed(packed, K, "mcg")), enc[f"mcg_K{K}_dq"])           # wrapped decode == encoder dq
 
 
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_decode_matvec_against_oracle_decode(q, oracle, name, K):
+    """y = x Zq^T from packed words alone (web/kernels.js:105-128) against the oracle's window decode of the same words
+    followed by an fp64 product.  Every bit pattern is a valid code stream, so the words are random.  Floating point:
+    fp32 accumulation in a different order from the fp64 check, tolerance 2e-6 of the result's norm per right-hand side."""
+    n_out, k_in = 48, 80                                   # 3 x 5 tiles: an odd tile count per row leaves half a warp idle
+    rng = np.random.default_rng(K * 10 + len(name))
+    packed_np = rng.integers(0, 2 ** 32, size=(n_out // 16 * (k_in // 16), 8 * K), dtype=np.uint64).astype(np.uint32)
+    zq = oracle.decode_packed(packed_np, K, name).reshape(n_out // 16, k_in // 16, 16, 16).transpose(0, 2, 1, 3).reshape(n_out, k_in)
+    packed = torch.from_numpy(packed_np.view(np.int32)).cuda()
+    for m in (1, 2, 3, 4, 5, 9):
+        x = torch.randn(m, k_in, generator=torch.Generator().manual_seed(m))
+        want = x.double().numpy() @ zq.astype(np.float64).T
+        got = _np(q.decode_matvec(packed, n_out, k_in, K, name, x.cuda())).astype(np.float64)
+        assert got.shape == (m, n_out)
+        err = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+        assert err.max() < 2e-6, (m, err)
+    x1 = torch.randn(k_in, generator=torch.Generator().manual_seed(7))
+    y1 = q.decode_matvec(packed, n_out, k_in, K, name, x1.cuda())
+    assert y1.shape == (n_out,)
+    assert torch.equal(y1, q.decode_matvec(packed, n_out, k_in, K, name, x1.cuda()))            # reproducible
+    assert torch.equal(y1, q.decode_matvec(packed, n_out, k_in, K, name, x1.cuda()[None])[0])
+    host = q.decode_matvec(packed.cpu(), n_out, k_in, K, name, x1)                               # host tensors in, host out
+    assert not host.is_cuda and torch.equal(host, y1.cpu())
+
+
+def test_decode_matvec_on_encoder_output_equals_dense_product(q):
+    """Encode a matrix's tiles, then multiply from the packed words: equals the dense product with the decoded matrix."""
+    torch.manual_seed(3)
+    n_out, k_in = 256, 1024
+    z = torch.randn(n_out, k_in, device="cuda")
+    r = q.encode(q.to_tiles(z).contiguous(), 3, "3inst", want_dq=True)
+    zq = q.from_tiles(r.dq, n_out, k_in)
+    x = torch.randn(4, k_in, device="cuda")
+    got = q.decode_matvec(r.packed, n_out, k_in, 3, "3inst", x)
+    want = (x.double() @ zq.double().t())
+    assert float((got.double() - want).norm() / want.norm()) < 2e-6
+    with pytest.raises(ValueError):
+        q.decode_matvec(r.packed, n_out, k_in + 16, 3, "3inst", x)
+    with pytest.raises(ValueError):
+        q.decode_matvec(r.packed, n_out, k_in, 3, "3inst", x[:, :-16])
+    assert q.decode_matvec(r.packed, n_out, k_in, 3, "3inst", x[:0]).shape == (0, n_out)
+
+
 def test_tailbiting_stream_wraps(q):
     # tests/test_qtip.py:48-68: exactly K bits per weight, and the symbols alone reproduce dq
     torch.manual_seed(1)

@@ -302,6 +302,21 @@ int tcq_decode_packed(const uint32_t* packed, int64_t n_tiles, int K, int codebo
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "decode_packed");
 }
 
+int tcq_decode_matvec(const uint32_t* packed, int64_t n_out, int64_t k_in, int K, int codebook, const float* x, int64_t ldx,
+                      int m, float* y, int64_t ldy, void* stream) {
+    int rc = check_common(K, codebook, n_out);
+    if (rc != TCQ_OK) return rc;
+    if (k_in < 0 || m < 0) return TCQ_E_BAD_COUNT;
+    if (n_out % 16 || k_in % 16 || n_out / 16 > 0x7FFFFFFF || k_in / 16 > 0x7FFFFFFF) return TCQ_E_BAD_ARGUMENT;
+    if (n_out == 0 || k_in == 0 || m == 0) return TCQ_OK;
+    if (ldx < k_in || ldx % 4 || ldy < n_out) return TCQ_E_BAD_ARGUMENT;
+    if (packed == nullptr || x == nullptr || y == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(packed, 4) || misaligned(x, 16) || misaligned(y, 4)) return TCQ_E_MISALIGNED;
+    cudaError_t err = launch_decode_matvec(packed, n_out, k_in, K, codebook, x, ldx, m, y, ldy,
+                                           static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "decode_matvec");
+}
+
 int tcq_decode_symbols(const int64_t* bits, int64_t n, int64_t T, int K, int codebook, const int64_t* s0, float* out,
                        void* stream) {
     int rc = check_common(K, codebook, n);

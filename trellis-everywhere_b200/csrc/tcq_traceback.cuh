@@ -24,6 +24,8 @@ cudaError_t launch_traceback(int K, const TracebackArgs& args, cudaStream_t stre
 
 // Decode / packing kernels (tcq_decode.cu).
 cudaError_t launch_decode_packed(const uint32_t* packed, long long n, int K, int codebook, float* dq, cudaStream_t stream);
+cudaError_t launch_decode_matvec(const uint32_t* packed, long long n_out, long long k_in, int K, int codebook, const float* x,
+                                 long long ldx, int m, float* y, long long ldy, cudaStream_t stream);
 cudaError_t launch_decode_symbols(const long long* bits, long long n, long long T, int K, int codebook,
                                   const long long* s0, float* out, cudaStream_t stream);
 cudaError_t launch_pack_symbols(const long long* bits, long long n, int K, uint32_t* packed, cudaStream_t stream);

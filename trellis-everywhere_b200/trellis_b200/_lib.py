@@ -32,6 +32,7 @@ SIGNATURES = {
     "tcq_selftest_wait_timeout": (_int, [_vp, _i64, _int, _vp, _sz, _vp]),
     "tcq_encode_launches": (_i64, [_i64, _int, _sz]),
     "tcq_decode_packed": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
+    "tcq_decode_matvec": (_int, [_vp, _i64, _i64, _int, _int, _vp, _i64, _int, _vp, _i64, _vp]),
     "tcq_decode_symbols": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "tcq_pack_symbols": (_int, [_vp, _i64, _int, _vp, _vp]),
     "tcq_codebook_lut": (_int, [_int, _vp, _vp]),

@@ -117,6 +117,7 @@ def codebook_lut(name: str, device="cpu") -> torch.Tensor:
         lut = torch.empty(S, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().tcq_codebook_lut(CODEBOOK_IDS[name], lut.data_ptr(), _stream(dev)), "tcq_codebook_lut")
+            torch.cuda.current_stream(dev).synchronize()      # other streams (threads) read the cached table
         _lut_cache[key] = lut
     return lut.to(device).clone()
 
@@ -353,6 +354,42 @@ def decode_packed(packed: torch.Tensor, K: int, codebook: CodebookLike) -> torch
             rc = _lib.lib().tcq_decode_packed(pd.data_ptr(), n, K, cid, dq.data_ptr(), _stream(dev))
         _lib.check(rc, "tcq_decode_packed")
     return dq if packed.is_cuda else dq.cpu()
+
+
+@torch.no_grad()
+def decode_matvec(packed: torch.Tensor, n_out: int, k_in: int, K: int, codebook: CodebookLike, x: torch.Tensor) -> torch.Tensor:
+    """``x @ Zq.T`` straight from packed codes: ``x [k_in]`` or ``[m, k_in]`` -> ``[n_out]`` or ``[m, n_out]`` fp32.
+
+    ``Zq`` is the ``[n_out, k_in]`` code matrix in the exporter's tile order (tile ``(row/16)*(k_in/16) + col/16``);
+    it is decoded on the fly and never stored.  CUDA form of the reference's DECODE_MATMUL shader
+    (web/kernels.js:105-128); the incoherence-processing fold stays with the caller (``shards.packed_linear``).
+    """
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    if n_out % 16 or k_in % 16 or n_out < 0 or k_in < 0:
+        raise ValueError(f"n_out={n_out} and k_in={k_in} must be non-negative multiples of 16")
+    tiles = (n_out // 16) * (k_in // 16)
+    if packed.dim() != 2 or tuple(packed.shape) != (tiles, T_SEQ * K // 32):
+        raise ValueError(f"expected packed words of shape [{tiles}, {T_SEQ * K // 32}], got {tuple(packed.shape)}")
+    if packed.dtype not in (torch.int32, torch.uint32):
+        raise ValueError("packed words must be int32 or uint32")
+    if x.dim() not in (1, 2) or x.shape[-1] != k_in:
+        raise ValueError(f"x must be [{k_in}] or [m, {k_in}], got {tuple(x.shape)}")
+    cid = codebook_id(codebook)
+    dev = _cuda_device(packed if packed.is_cuda else (x if x.is_cuda else None))
+    pd = _to_dev(packed.view(torch.int32), dev, torch.int32)
+    xd = _to_dev(x.reshape(-1, k_in), dev, torch.float32)
+    m = xd.shape[0]
+    y = torch.empty((m, n_out), dtype=torch.float32, device=dev)
+    if k_in == 0:
+        y.zero_()
+    elif m and n_out:
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_decode_matvec(pd.data_ptr(), n_out, k_in, K, cid, xd.data_ptr(), k_in, m, y.data_ptr(), n_out,
+                                              _stream(dev))
+        _lib.check(rc, "tcq_decode_matvec")
+    y = y.reshape(*x.shape[:-1], n_out)
+    return y if (packed.is_cuda or x.is_cuda) else y.cpu()
 
 
 @torch.no_grad()

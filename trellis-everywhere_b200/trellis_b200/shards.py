@@ -123,7 +123,8 @@ def read_quant(out_dir: str, manifest: Dict[str, dict], name: str) -> dict:
 @torch.no_grad()
 def packed_linear(q: dict, x: torch.Tensor, codebook="mcg", device=None) -> torch.Tensor:
     """``y = W_hat x`` from a ``read_quant`` record, the way the reference's runtime folds the restore
-    (``web/packed.js:163-182``); ``x`` is ``[k_in]`` or ``[k_in, m]``.  The decode runs on the GPU."""
+    (``web/packed.js:163-182``); ``x`` is ``[k_in]`` or ``[k_in, m]``.  The product with the code matrix is the
+    CUDA decode-matvec kernel (``qtip.decode_matvec``)."""
     dev = torch.device(device) if device is not None else qtip._cuda_device(x if x.is_cuda else None)
     n, k, K = q["n_out"], q["k_in"], q["K"]
     f = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.float32)).to(dev)
@@ -131,8 +132,8 @@ def packed_linear(q: dict, x: torch.Tensor, codebook="mcg", device=None) -> torc
     xf = col * (f(q["su"]) * f(q["isc"]) * float(q["scale"][0]))[:, None]
     xf = qtip.block_hadamard(xf, 0, q["block"])
     packed = torch.from_numpy(np.ascontiguousarray(q["bits"]).view(np.int32)).to(dev)
-    zq = qtip.from_tiles(qtip.decode_packed(packed, K, codebook), n, k)
-    t = qtip.block_hadamard(zq @ xf, 0, qtip._pow2_block(n, 128))
+    prod = qtip.decode_matvec(packed, n, k, K, codebook, xf.t().contiguous()).t()       # [n, m]; the code matrix is never formed
+    t = qtip.block_hadamard(prod, 0, qtip._pow2_block(n, 128))
     y = t * (f(q["osc"]) * f(q["sv"]))[:, None]
     return y.reshape(n, *x.shape[1:])
 
