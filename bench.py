@@ -114,7 +114,7 @@ def make_tiles(torch, qtip, device, seed: int):
     w = torch.where(mask, w * 20, w)
     lut = qtip.codebook_lut(CODEBOOK, device)
     ip = qtip.IPContext(w, lut.square().mean().sqrt().item(), seed=0)
-    return qtip.to_tiles(ip.z).contiguous()
+    return ip.tiles
 
 
 def cpu_port_rate(tiles_np, seconds: float, threads: int):
@@ -411,6 +411,67 @@ def run_decode_matvec(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_ip(args) -> None:
+    """Side measurement of the incoherence-processing kernels (the producer of the encoder's tiles and the consumer of
+    its reconstruction) through the C ABI with preallocated buffers: forward = 20 algorithmic bytes per weight (w read
+    twice, one intermediate written and read, tiles written), restore = 16."""
+    import torch
+    from trellis_b200 import _lib, qtip
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n, k = args.n_out if args.n_out != 151936 else 12288, args.k_in
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = torch.randn(n, k, device=dev, generator=g) * 0.02
+    ip = qtip.IPContext(w, 0.9, seed=0)
+    L = _lib.lib()
+    ws = torch.empty(int(L.tcq_ip_workspace_bytes(n, k)), dtype=torch.uint8, device=dev)
+    tiles, out = torch.empty_like(ip.tiles), torch.empty_like(w)
+    out_s, in_s, scale = torch.empty_like(ip.out_s), torch.empty_like(ip.in_s), torch.empty(1, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def fwd():
+        _lib.check(L.tcq_ip_forward(w.data_ptr(), n, k, ip.sv.data_ptr(), ip.su.data_ptr(), 0.9, 1, tiles.data_ptr(), out_s.data_ptr(),
+                                    in_s.data_ptr(), scale.data_ptr(), ws.data_ptr(), ws.numel(), st), "tcq_ip_forward")
+
+    def inv():
+        _lib.check(L.tcq_ip_restore(tiles.data_ptr(), 1, n, k, ip.sv.data_ptr(), ip.su.data_ptr(), out_s.data_ptr(), in_s.data_ptr(),
+                                    scale.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st), "tcq_ip_restore")
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    with ClockSampler(0) as clocks:
+        ms_f, ms_i = timed(fwd), timed(inv)
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            fwd()
+        torch.cuda.synchronize()
+    err = float((out - w).norm() / w.norm())
+    hbm = measured_peaks().get("hbm_gbs") or 6650.0
+    gbs_f, gbs_i = n * k * 20 / (ms_f * 1e-3) / 1e9, n * k * 16 / (ms_i * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "weights incoherence-processed/sec (forward)", "value": n * k / (ms_f * 1e-3), "unit": "weights/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_f, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"SIDE MEASUREMENT: incoherence processing of a [{n}, {k}] fp32 matrix ({n * k * 4 / 2 ** 20:.0f} MiB, larger "
+                               "than L2) through tcq_ip_forward / tcq_ip_restore, buffers preallocated", "n": n, "k": k},
+        "restore": {"ms_per_step": ms_i, "weights_per_s": n * k / (ms_i * 1e-3), "round_trip_rel_err": err},
+        "gpu_launches": 5 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "ip_row_sumsq + ip_had_rows + ip_had_cols (forward, 5 launches)", "achieved": gbs_f,
+                     "peak": hbm, "unit": "GB/s", "frac": gbs_f / hbm, "traffic": None,
+                     "restore": {"achieved": gbs_i, "frac": gbs_i / hbm}},
+        "clocks": clocks.summary()}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,8 +485,9 @@ def main() -> None:
                     help="bits per weight; anything but the default 3 is a side measurement, not the benchmark")
     ap.add_argument("--codebook", default="3inst", choices=("1mad", "3inst", "mcg"),
                     help="codebook; anything but the default 3inst is a side measurement, not the benchmark")
-    ap.add_argument("--path", choices=("encode", "decode_matvec"), default="encode",
-                    help="encode = the benchmark; decode_matvec = side measurement of the packed format's consumer kernel")
+    ap.add_argument("--path", choices=("encode", "decode_matvec", "ip"), default="encode",
+                    help="encode = the benchmark; decode_matvec / ip = side measurements of the packed format's consumer kernel "
+                         "and of the incoherence-processing kernels")
     ap.add_argument("--n-out", type=int, default=151936, help="decode_matvec: output rows (default: lm_head of the model shape)")
     ap.add_argument("--k-in", type=int, default=4096, help="decode_matvec: input columns")
     ap.add_argument("--m", type=int, default=1, help="decode_matvec: right-hand sides")
@@ -438,11 +500,11 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.path == "decode_matvec":
+    if args.path != "encode":
         if args.impl != "b200" or args.gpus != 1:
-            raise SystemExit("--path decode_matvec is a one-GPU side measurement of this library")
+            raise SystemExit(f"--path {args.path} is a one-GPU side measurement of this library")
         if rank == 0:
-            run_decode_matvec(args)
+            (run_decode_matvec if args.path == "decode_matvec" else run_ip)(args)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:

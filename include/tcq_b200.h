@@ -188,6 +188,29 @@ TCQ_API int tcq_decode_matvec(const uint32_t *packed, int64_t n_out, int64_t k_i
                       int64_t ldx, int m, float *y, int64_t ldy, void *stream);
 
 /*
+ * Incoherence processing on the device.  Replaces IPContext.__init__ / IPContext.restore
+ * (src/trellis/qtip.py:238-268): row signs sv and column signs su (+-1, drawn by the
+ * caller so that the reference's seeded CPU generator stays the source), per-row RMS
+ * scales out_s and block-Hadamard over the row axis, per-column RMS scales in_s and
+ * block-Hadamard over the column axis (blocks: largest power of two <= 128 dividing the
+ * axis, qtip.py:208-223; fast Walsh-Hadamard transform instead of the dense matrix of
+ * qtip.py:216-223), then one global scale so that z has RMS cb_rms.
+ *   tcq_ip_forward:  w [n,k] fp32 -> z (tiled != 0: [n/16*k/16, 256] in the encoder's tile
+ *                    order, qtip.py:288; tiled == 0: [n,k]), out_s [n], in_s [k], scale [1]
+ *                    (all device memory; scale stays on the device so nothing synchronises)
+ *   tcq_ip_restore:  zq (same two layouts) -> w_hat [n,k]
+ *   n, k multiples of 16, n <= 16 * 65535;  z, zq and in_s 16-byte aligned;
+ *   ws: tcq_ip_workspace_bytes(n,k) bytes, 256-byte aligned
+ * Floating point: equal to the reference's matmul form up to fp32 summation order.
+ */
+TCQ_API size_t tcq_ip_workspace_bytes(int64_t n, int64_t k);
+TCQ_API int tcq_ip_forward(const float *w, int64_t n, int64_t k, const float *sv, const float *su, float cb_rms, int tiled,
+                   float *z, float *out_s, float *in_s, float *scale, void *ws, size_t ws_bytes, void *stream);
+TCQ_API int tcq_ip_restore(const float *zq, int tiled, int64_t n, int64_t k, const float *sv, const float *su,
+                   const float *out_s, const float *in_s, const float *scale, float *w_hat, void *ws, size_t ws_bytes,
+                   void *stream);
+
+/*
  * Decode unpacked symbol streams of any length T (no wrap): state_t is the last
  * 16 bits of s0 followed by symbols 0..t.  Replaces decode_recursive and
  * decode_window (src/trellis/qtip.py:70-110), which are equal by construction.

@@ -400,3 +400,46 @@ def test_non_finite_weights_are_flagged_not_trapped(q):
         q.workspace_status(10, 3)
     q.encode(w, 3, "mcg")
     q.workspace_status(10, 3)                                  # the flag is per call
+
+
+@pytest.mark.parametrize("shape", [(128, 256), (48, 80), (256, 96), (32, 64), (1024, 2048)])
+def test_device_incoherence_processing_matches_the_matmul_form(q, shape):
+    """tcq_ip_forward / tcq_ip_restore (fast Walsh-Hadamard kernels) against the PyTorch restatement of
+    qtip.py:238-268 run on the host (dense Hadamard matmul).  Floating point: summation order differs, so the
+    scale vectors agree to 1e-5 relative and z to 3e-5 absolute (z has RMS ~0.5-1)."""
+    n, k = shape
+    g = torch.Generator().manual_seed(n + k)
+    w = torch.randn(n, k, generator=g) * 0.02
+    w[::7, ::5] *= 20                                                   # outliers, as in the benchmark matrix
+    cb_rms = q.codebook_lut("mcg").square().mean().sqrt().item()
+    host = q.IPContext(w, cb_rms, seed=3)
+    dev = q.IPContext(w.cuda(), cb_rms, seed=3)
+    assert dev.on_device and not host.on_device
+    assert torch.equal(dev.sv.cpu(), host.sv) and torch.equal(dev.su.cpu(), host.su)
+    assert torch.allclose(dev.out_s.cpu(), host.out_s, rtol=1e-5) and torch.allclose(dev.in_s.cpu(), host.in_s, rtol=1e-5)
+    assert abs(dev.scale - host.scale) <= 1e-5 * host.scale
+    assert float((dev.z.cpu() - host.z).abs().max()) < 3e-5
+    assert torch.equal(dev.tiles, q.to_tiles(dev.z).contiguous())       # tile order of qtip.py:288
+    assert abs(float(dev.z.square().mean().sqrt()) - cb_rms) < 1e-5 * cb_rms
+    # restore inverts forward, from either layout, and matches the host restore of the same input
+    back = dev.restore(dev.z)
+    assert float((back.cpu() - w).norm() / w.norm()) < 2e-6
+    assert torch.equal(dev.restore_tiles(dev.tiles), back)
+    zq = torch.randn(n, k, generator=g)
+    assert float((dev.restore(zq.cuda()).cpu() - host.restore(zq)).norm() / host.restore(zq).norm()) < 2e-6
+    again = q.IPContext(w.cuda(), cb_rms, seed=3)                        # fixed-order reductions: reproducible
+    assert torch.equal(again.tiles, dev.tiles) and torch.equal(again.in_s, dev.in_s) and again.scale == dev.scale
+    with pytest.raises(ValueError):
+        dev.restore(zq[:, :-16].cuda())
+
+
+def test_device_incoherence_processing_against_reference_vectors(q, golden):
+    """The vectors the reference's IPContext produced for the shard golden (seed crc32(b"x"))."""
+    import zlib
+    g = golden["shard"]
+    cb_rms = q.codebook_lut("mcg").square().mean().sqrt().item()
+    ip = q.IPContext(torch.from_numpy(g["w"]).cuda(), cb_rms, seed=zlib.crc32(b"x"))
+    assert ip.on_device
+    assert np.array_equal(_np(ip.su), g["su"]) and np.array_equal(_np(ip.sv), g["sv"])
+    assert np.allclose(_np(ip.in_s), g["in_s"], rtol=1e-5) and np.allclose(_np(ip.out_s), g["out_s"], rtol=1e-5)
+    assert abs(ip.scale - float(g["scale"])) < 1e-5 * float(g["scale"])

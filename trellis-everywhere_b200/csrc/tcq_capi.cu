@@ -342,6 +342,50 @@ int tcq_pack_symbols(const int64_t* bits, int64_t n_tiles, int K, uint32_t* pack
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "pack_symbols");
 }
 
+namespace {
+int check_ip_shape(int64_t n, int64_t k) {
+    if (n < 0 || k < 0) return TCQ_E_BAD_COUNT;
+    if (n % 16 || k % 16 || n / 16 > 65535) return TCQ_E_BAD_ARGUMENT;
+    return TCQ_OK;
+}
+}  // namespace
+
+size_t tcq_ip_workspace_bytes(int64_t n, int64_t k) {
+    if (check_ip_shape(n, k) != TCQ_OK || n == 0 || k == 0) return 0;
+    return ip_workspace_bytes(n, k);
+}
+
+int tcq_ip_forward(const float* w, int64_t n, int64_t k, const float* sv, const float* su, float cb_rms, int tiled,
+                   float* z, float* out_s, float* in_s, float* scale, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_ip_shape(n, k);
+    if (rc != TCQ_OK) return rc;
+    if (!(cb_rms > 0.0f)) return TCQ_E_BAD_ARGUMENT;
+    if (n == 0 || k == 0) return TCQ_OK;
+    if (!w || !sv || !su || !z || !out_s || !in_s || !scale || !ws) return TCQ_E_NULL_POINTER;
+    if (misaligned(w, 4) || misaligned(z, 16) || misaligned(sv, 4) || misaligned(su, 4) || misaligned(out_s, 4) ||
+        misaligned(in_s, 16) || misaligned(scale, 4) || misaligned(ws, 256))
+        return TCQ_E_MISALIGNED;
+    if (ws_bytes < ip_workspace_bytes(n, k)) return TCQ_E_WORKSPACE;
+    cudaError_t err = launch_ip_forward(w, n, k, sv, su, cb_rms, tiled != 0, z, out_s, in_s, scale, ws,
+                                        static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "ip_forward");
+}
+
+int tcq_ip_restore(const float* zq, int tiled, int64_t n, int64_t k, const float* sv, const float* su, const float* out_s,
+                   const float* in_s, const float* scale, float* w_hat, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_ip_shape(n, k);
+    if (rc != TCQ_OK) return rc;
+    if (n == 0 || k == 0) return TCQ_OK;
+    if (!zq || !sv || !su || !out_s || !in_s || !scale || !w_hat || !ws) return TCQ_E_NULL_POINTER;
+    if (misaligned(zq, 16) || misaligned(w_hat, 4) || misaligned(sv, 4) || misaligned(su, 4) || misaligned(out_s, 4) ||
+        misaligned(in_s, 16) || misaligned(scale, 4) || misaligned(ws, 256))
+        return TCQ_E_MISALIGNED;
+    if (ws_bytes < ip_workspace_bytes(n, k)) return TCQ_E_WORKSPACE;
+    cudaError_t err = launch_ip_restore(zq, tiled != 0, n, k, sv, su, out_s, in_s, scale, w_hat, ws,
+                                        static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "ip_restore");
+}
+
 int tcq_codebook_lut(int codebook, float* lut, void* stream) {
     if (codebook < 0 || codebook > 2) return TCQ_E_BAD_CODEBOOK;
     if (lut == nullptr) return TCQ_E_NULL_POINTER;

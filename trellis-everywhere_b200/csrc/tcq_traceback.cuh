@@ -31,4 +31,12 @@ cudaError_t launch_decode_symbols(const long long* bits, long long n, long long 
 cudaError_t launch_pack_symbols(const long long* bits, long long n, int K, uint32_t* packed, cudaStream_t stream);
 cudaError_t launch_codebook_lut(int codebook, float* lut, cudaStream_t stream);
 
+// Incoherence processing (tcq_ip.cu).
+size_t ip_workspace_bytes(long long n, long long k);
+cudaError_t launch_ip_forward(const float* w, long long n, long long k, const float* sv, const float* su, float cb_rms,
+                              int tiled, float* z_out, float* out_s, float* in_s, float* scale, void* ws, cudaStream_t stream);
+cudaError_t launch_ip_restore(const float* zq, int tiled, long long n, long long k, const float* sv, const float* su,
+                              const float* out_s, const float* in_s, const float* scale, float* w_hat, void* ws,
+                              cudaStream_t stream);
+
 }  // namespace tcq

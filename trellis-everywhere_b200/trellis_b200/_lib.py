@@ -36,6 +36,9 @@ SIGNATURES = {
     "tcq_decode_symbols": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "tcq_pack_symbols": (_int, [_vp, _i64, _int, _vp, _vp]),
     "tcq_codebook_lut": (_int, [_int, _vp, _vp]),
+    "tcq_ip_workspace_bytes": (_sz, [_i64, _i64]),
+    "tcq_ip_forward": (_int, [_vp, _i64, _i64, _vp, _vp, ctypes.c_float, _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "tcq_ip_restore": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -92,8 +92,8 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
     ip = qtip.IPContext(w.float(), lut.square().mean().sqrt().item(), seed=seed)
     nw = qtip.T_SEQ * K // 32
     if H is None:
-        r = qtip.encode(qtip.to_tiles(ip.z).contiguous(), K, codebook, want_dq=True, want_sse=False)
-        packed, zq = r.packed, qtip.from_tiles(r.dq, n, k)
+        r = qtip.encode(ip.tiles, K, codebook, want_dq=True, want_sse=False)
+        packed, w_hat = r.packed, ip.restore_tiles(r.dq)
     else:
         Ht = tldlq._transform_H(H.float(), ip.su, block=qtip._pow2_block(k, 128))
         with _linalg_lock:                 # torch's lazily initialised linalg backends must not be entered by two threads at once
@@ -110,7 +110,7 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
         zq = tldlq.ldlq(ip.z.t().contiguous(), Lm, tldlq.make_enc(K, codebook, sink)).t().contiguous()
         assert col[0] == 0
         packed = store.reshape(-1, nw)
-    w_hat = ip.restore(zq)
+        w_hat = ip.restore(zq)
     rel = float(((w - w_hat) ** 2).mean() / w.square().mean())
     return packed, w_hat, rel
 

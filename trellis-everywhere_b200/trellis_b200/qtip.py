@@ -469,15 +469,37 @@ class IPContext:
     out axis first), per-output-channel RMS scaling + block-Hadamard over the out axis,
     per-input-channel RMS scaling + block-Hadamard over the in axis, then one global
     scale so that ``z`` has the codebook's RMS.  ``restore`` inverts every step.
-    Stays in PyTorch: it is outside the encoder hot path.
+
+    For a CUDA matrix (16-divisible shape, default block) the work is done by the library's
+    kernels (``tcq_ip_forward`` / ``tcq_ip_restore``: fast Walsh-Hadamard transforms, output
+    directly in the encoder's tile order); ``tiles`` is then the primary result and ``z`` is
+    formed from it on first use, and ``scale`` is read back from the device on first use.
+    Host tensors, odd shapes and other block sizes take the PyTorch restatement below.
     """
 
     def __init__(self, w: torch.Tensor, cb_rms: float, seed: int = 0, block: int = 128):
         gen = torch.Generator(device="cpu").manual_seed(seed)
         n, k = w.shape
         self.block = block
+        self.shape = (n, k)
         self.sv = (torch.randint(0, 2, (n,), generator=gen).float() * 2 - 1).to(w.device)
         self.su = (torch.randint(0, 2, (k,), generator=gen).float() * 2 - 1).to(w.device)
+        self._z = self._tiles = self._scale = self._scale_t = None
+        self.on_device = bool(w.is_cuda and block == 128 and n % 16 == 0 and k % 16 == 0 and 0 < n <= 16 * 65535 and k > 0)
+        if self.on_device:
+            dev = w.device
+            wd = w.to(torch.float32).contiguous()
+            self._tiles = torch.empty((n // 16 * (k // 16), T_SEQ), dtype=torch.float32, device=dev)
+            self.out_s = torch.empty(n, dtype=torch.float32, device=dev)
+            self.in_s = torch.empty(k, dtype=torch.float32, device=dev)
+            self._scale_t = torch.empty(1, dtype=torch.float32, device=dev)
+            ws = self._ip_workspace(dev)
+            with torch.cuda.device(dev):
+                rc = _lib.lib().tcq_ip_forward(wd.data_ptr(), n, k, self.sv.data_ptr(), self.su.data_ptr(), float(cb_rms), 1,
+                                               self._tiles.data_ptr(), self.out_s.data_ptr(), self.in_s.data_ptr(),
+                                               self._scale_t.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev))
+            _lib.check(rc, "tcq_ip_forward")
+            return
         z = w * self.sv[:, None] * self.su[None, :]
         out_s = z.square().mean(dim=1).sqrt().clamp_min(1e-8)
         self.out_s = out_s / out_s.mean()
@@ -485,13 +507,63 @@ class IPContext:
         in_s = z.square().mean(dim=0).sqrt().clamp_min(1e-8)
         self.in_s = in_s / in_s.mean()
         z = block_hadamard(z / self.in_s[None, :], 1, block)
-        self.scale = z.square().mean().sqrt().item() / cb_rms
-        self.z = z / self.scale
+        self._scale = z.square().mean().sqrt().item() / cb_rms
+        self._z = z / self._scale
+
+    def _ip_workspace(self, dev: torch.device) -> torch.Tensor:
+        n, k = self.shape
+        return torch.empty(int(_lib.lib().tcq_ip_workspace_bytes(n, k)), dtype=torch.uint8, device=dev)
+
+    @property
+    def scale(self) -> float:
+        if self._scale is None:
+            self._scale = float(self._scale_t.item())
+        return self._scale
+
+    @property
+    def z(self) -> torch.Tensor:
+        """The processed matrix ``[n, k]``."""
+        if self._z is None:
+            self._z = from_tiles(self._tiles, *self.shape).contiguous()
+        return self._z
+
+    @property
+    def tiles(self) -> torch.Tensor:
+        """The processed matrix as encoder tiles ``[n/16 * k/16, 256]`` (qtip.py:288)."""
+        if self._tiles is None:
+            self._tiles = to_tiles(self._z).contiguous()
+        return self._tiles
+
+    def _restore_device(self, zq: torch.Tensor, tiled: bool) -> torch.Tensor:
+        n, k = self.shape
+        dev = self.sv.device
+        zd = zq.to(device=dev, dtype=torch.float32).contiguous()
+        out = torch.empty((n, k), dtype=torch.float32, device=dev)
+        ws = self._ip_workspace(dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tcq_ip_restore(zd.data_ptr(), int(tiled), n, k, self.sv.data_ptr(), self.su.data_ptr(),
+                                           self.out_s.data_ptr(), self.in_s.data_ptr(), self._scale_t.data_ptr(),
+                                           out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev))
+        _lib.check(rc, "tcq_ip_restore")
+        return out
 
     def restore(self, zq: torch.Tensor) -> torch.Tensor:
+        if self.on_device:
+            if tuple(zq.shape) != self.shape:
+                raise ValueError(f"expected a {self.shape} matrix, got {tuple(zq.shape)}")
+            return self._restore_device(zq, tiled=False)
         y = block_hadamard(zq * self.scale, 1, self.block) * self.in_s[None, :]
         y = block_hadamard(y, 0, self.block) * self.out_s[:, None]
         return y * self.sv[:, None] * self.su[None, :]
+
+    def restore_tiles(self, dq: torch.Tensor) -> torch.Tensor:
+        """``restore`` of a reconstruction still in tile order ``[n/16 * k/16, 256]`` (skips the untiling copy)."""
+        n, k = self.shape
+        if tuple(dq.shape) != (n // 16 * (k // 16), T_SEQ):
+            raise ValueError(f"expected [{n // 16 * (k // 16)}, {T_SEQ}] tiles, got {tuple(dq.shape)}")
+        if self.on_device:
+            return self._restore_device(dq, tiled=True)
+        return self.restore(from_tiles(dq, n, k))
 
 
 def to_tiles(z: torch.Tensor) -> torch.Tensor:
@@ -530,6 +602,6 @@ def tcq_quantize_weight(w: torch.Tensor, K: int, lut: CodebookLike, seed: int = 
     lut_t = lut if isinstance(lut, torch.Tensor) else codebook_lut(CODEBOOK_NAMES[codebook_id(lut)], dev)
     cb_rms = lut_t.float().square().mean().sqrt().item()
     ip = IPContext(wd.float(), cb_rms, seed=seed)
-    tiles = to_tiles(ip.z).contiguous()
+    tiles = ip.tiles
     dq = encode(tiles, K, lut, want_dq=True, want_sse=False).dq
-    return ip.restore(from_tiles(dq, n, k)).to(dtype=w.dtype, device=w.device)
+    return ip.restore_tiles(dq).to(dtype=w.dtype, device=w.device)
