@@ -161,3 +161,23 @@ def test_shard_from_the_gpu_encoder_equals_the_reference_shard_and_evaluates(mod
     assert y.shape == (n, 3)
     assert float((y - want).norm() / want.norm()) < 2e-3          # fp16 scale vectors
     assert torch.allclose(shards.packed_linear(rec, x[:, 0]).cpu(), y[:, 0], rtol=1e-5, atol=1e-7)
+
+
+def test_ldlq_row_groups_side_by_side(mods, golden):
+    """Slices of output channels run as separate recursions on separate streams: the packed words still decode to the
+    returned W_hat, and the Hessian objective equals the single recursion's (identical unless a feedback GEMM's
+    summation order differs between the column counts; tolerance 2 %)."""
+    q, l = mods
+    from trellis_b200 import model
+    g = golden["ldlq"]
+    w = torch.from_numpy(g["w"]).cuda()                                   # 64 x 256
+    H = torch.from_numpy(g["H"]).cuda()
+    p1, w1, _ = model.encode_matrix(w, 3, "mcg", 0, H)
+    p3, w3, _ = model.encode_matrix(w, 3, "mcg", 0, H, row_groups=3)      # slices of 32, 32 and 0 -> two groups of rows
+    lut = q.codebook_lut("mcg", "cuda")
+    ip = q.IPContext(w, lut.square().mean().sqrt().item(), seed=0)
+    assert torch.equal(ip.restore_tiles(q.decode_packed(p3, 3, "mcg")), w3)
+    obj = lambda wh: float(torch.trace((wh - w) @ H @ (wh - w).t()))
+    assert abs(obj(w3) - obj(w1)) <= 0.02 * obj(w1)
+    ld = l.tcq_quantize_weight_ldlq(w, K=3, lut="mcg", H=H, seed=0, row_groups=2)
+    assert abs(obj(ld) - obj(w1)) <= 0.02 * obj(w1)

@@ -85,6 +85,51 @@ def ldlq(Wt: torch.Tensor, L: torch.Tensor, enc: Callable[[torch.Tensor], torch.
     return Wq.to(Wt.dtype)
 
 
+@torch.no_grad()
+def ldlq_row_groups(Wt: torch.Tensor, L: torch.Tensor, make_enc_for: Callable[[int, int], Callable], groups: int = 2,
+                    buf: int = 128) -> torch.Tensor:
+    """``ldlq`` with the output channels (columns of ``Wt``) cut into ``groups`` slices that run side by side.
+
+    The recursion couples input channels only, so column slices of ``Wt`` are independent problems with the same
+    ``L``.  One recursion issues encoder calls of ``n/16`` tiles one after another, which rarely fill the last round
+    of SMs (256 tiles occupy 64 of a B200's 74 SM pairs); slices on separate CUDA streams (one host thread each) let
+    one slice's kernels take the SMs the other leaves idle.  ``make_enc_for(a, b)`` returns the ``enc`` closure for
+    columns ``a:b`` (16-aligned).  Equal to ``ldlq`` up to the summation order of the feedback GEMMs, whose
+    column count differs.
+    """
+    import threading
+    k, n = Wt.shape
+    groups = max(1, min(int(groups), n // 16))
+    if groups == 1:
+        return ldlq(Wt, L, make_enc_for(0, n), buf)
+    per = -(-(n // 16) // groups) * 16
+    bounds = [(a, min(a + per, n)) for a in range(0, n, per)]
+    out = torch.empty_like(Wt)
+    dev = Wt.device
+    caller = torch.cuda.current_stream(dev)
+    errors = []
+
+    def run(a: int, b: int) -> None:
+        try:
+            with torch.cuda.device(dev):
+                s = torch.cuda.Stream(dev)
+                s.wait_stream(caller)
+                with torch.cuda.stream(s):
+                    out[:, a:b] = ldlq(Wt[:, a:b].contiguous(), L, make_enc_for(a, b), buf)
+                s.synchronize()
+        except BaseException as e:          # surfaced by the caller below
+            errors.append(e)
+
+    threads = [threading.Thread(target=run, args=ab) for ab in bounds]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if errors:
+        raise errors[0]
+    return out
+
+
 def _transform_H(H: torch.Tensor, su: torch.Tensor, block: int = 128) -> torch.Tensor:
     """Bring the input-axis Hessian into incoherence-processed space: signs + block-Hadamard on both sides (ldlq.py:102-109)."""
     H = su[:, None] * H * su[None, :]
@@ -121,11 +166,13 @@ def make_enc(K: int, codebook: CodebookLike, sink: Optional[Callable] = None) ->
 
 @torch.no_grad()
 def tcq_quantize_weight_ldlq(w: torch.Tensor, K: int, lut: CodebookLike, H: torch.Tensor, seed: int = 0,
-                             sigma_reg: float = 0.025, dp_dtype=torch.float32, backend: str = "auto") -> torch.Tensor:
+                             sigma_reg: float = 0.025, dp_dtype=torch.float32, backend: str = "auto",
+                             row_groups: int = 1) -> torch.Tensor:
     """LDLQ variant of ``tcq_quantize_weight`` with the signature of ldlq.py:112-154.
 
     ``w (n_out, k_in)``; ``H (k_in, k_in)`` proxy Hessian in the original space.
-    ``dp_dtype`` is ignored (path metrics are always fp32).
+    ``dp_dtype`` is ignored (path metrics are always fp32).  ``row_groups`` > 1 (not in the reference) runs that
+    many slices of output channels side by side on separate streams (``ldlq_row_groups``).
     """
     _check_backend(backend)
     n, k = w.shape
@@ -139,5 +186,5 @@ def tcq_quantize_weight_ldlq(w: torch.Tensor, K: int, lut: CodebookLike, H: torc
     Lm = block_ldl(regularize_H(Ht, sigma_reg), b=16)
     if Lm is None:                                  # degenerate Hessian: no feedback for this matrix (ldlq.py:148-151)
         Lm = torch.zeros(k, k, device=dev)
-    zq_t = ldlq(ip.z.t().contiguous(), Lm, make_enc(K, lut))
+    zq_t = ldlq_row_groups(ip.z.t().contiguous(), Lm, lambda a, b: make_enc(K, lut), row_groups)
     return ip.restore(zq_t.t().contiguous()).to(dtype=w.dtype, device=w.device)

@@ -80,11 +80,12 @@ def synthetic_hessian(name: str, k: int, device, rows: int = 8192) -> torch.Tens
 
 @torch.no_grad()
 def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torch.Tensor] = None,
-                  sigma_reg: float = 0.025):
+                  sigma_reg: float = 0.025, row_groups: int = 1):
     """One matrix: returns (packed int32 [n_tiles, 8K] in the reference's tile order, W_hat, relative error).
 
     Plain: tiles ordered ``(row/16) * (k/16) + col/16`` (qtip.py:288).  LDLQ: the same order, assembled from the
-    per-row-block encoder calls as the reference's exporter does (export_packed_8b.py:114-131).
+    per-row-block encoder calls as the reference's exporter does (export_packed_8b.py:114-131); ``row_groups`` > 1
+    runs that many slices of output channels side by side (``ldlq.ldlq_row_groups``), for a matrix encoded alone.
     """
     n, k = w.shape
     dev = w.device
@@ -101,14 +102,17 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
         if Lm is None:
             Lm = torch.zeros(k, k, device=dev)
         store = torch.empty((n // 16, k // 16, nw), dtype=torch.int32, device=dev)
-        col = [k // 16]
 
-        def sink(p):                       # encoder calls arrive from the last 16-column block to the first
-            col[0] -= 1
-            store[:, col[0]] = p
+        def enc_for(a: int, b: int):       # output channels a:b; encoder calls arrive from the last 16-column block to the first
+            col = [k // 16]
 
-        zq = tldlq.ldlq(ip.z.t().contiguous(), Lm, tldlq.make_enc(K, codebook, sink)).t().contiguous()
-        assert col[0] == 0
+            def sink(p):
+                col[0] -= 1
+                store[a // 16:b // 16, col[0]] = p
+
+            return tldlq.make_enc(K, codebook, sink)
+
+        zq = tldlq.ldlq_row_groups(ip.z.t().contiguous(), Lm, enc_for, row_groups).t().contiguous()
         packed = store.reshape(-1, nw)
         w_hat = ip.restore(zq)
     rel = float(((w - w_hat) ** 2).mean() / w.square().mean())
