@@ -299,12 +299,16 @@ def test_encoding_a_reconstruction_is_lossless(q, golden):
     assert torch.equal(r.dq, dq) and float(r.sse.max()) == 0.0
 
 
-def test_full_size_properties(q):
-    """The second benchmark configuration's size (65 536 tiles, K=3, 3INST): properties that need no oracle."""
+def test_full_size_properties(q, oracle, luts):
+    """The second benchmark configuration's size (65 536 tiles, K=3, 3INST): properties that need no oracle, plus the
+    oracle itself on 256 tiles spread over the whole batch (every chunk and every position within a tile group)."""
     g = torch.Generator(device="cuda").manual_seed(0)
     w = torch.randn(65536, 256, generator=g, device="cuda") * 1.2437
-    r = q.encode(w, 3, "3inst")
+    r = q.encode(w, 3, "3inst", want_bits=True)
     torch.cuda.synchronize()
+    idx = torch.arange(0, 65536, 257, device="cuda")[:256]
+    bits, dq_o, sse_o = oracle.viterbi_tb(_np(w[idx]), 3, luts["3inst"], with_sse=True)
+    assert np.array_equal(_np(r.bits[idx]), bits) and same_bits(_np(r.dq[idx]), dq_o) and same_bits(_np(r.sse[idx]), sse_o)
     dq = q.decode_packed(r.packed, 3, "3inst")
     assert torch.equal(dq, r.dq)                                         # encode -> packed -> decode round trip
     sse = ((w - dq).double() ** 2).sum(dim=1)
@@ -320,7 +324,7 @@ def test_full_size_properties(q):
 @pytest.mark.parametrize("K", [2, 3])
 def test_matrix_quantizer_against_reference_result(q, golden, K):
     """tcq_quantize_weight end to end against the reference's own W_hat (fp32 DP, CPU).  The incoherence
-    processing runs in PyTorch on the GPU here and on the CPU there, so the tiles differ in the last ulp and a
+    processing runs in the library's kernels here and in PyTorch on the CPU there, so the tiles differ in the last ulps and a
     few codes may flip (each flip is smeared over a 128 x 128 block by the inverse Hadamard); tolerance:
     quantisation error of the two results within 1 % of each other, and their difference below 1e-3 of the
     result's energy (a handful of flipped codes out of 32 768 gives about 3e-5)."""
