@@ -14,27 +14,38 @@ namespace {
 // tests/test_qtip.py:55-67 and WGSL wz() (web/kernels.js:115-122): weight t is the
 // codebook value of the window that starts at stream bit (255-t)*K; the window of
 // the first few weights runs past the last word and continues at word 0.
-// One thread decodes four consecutive weights and stores them as one float4.
-template <int K>
+// One warp decodes one tile: lane l takes the eight weights t = 8l .. 8l+7, whose windows lie in
+// 7K+16 consecutive stream bits (three words at most, loaded once), and stores them as two float4;
+// the warp reads the tile's 32K bytes and writes its 1 KiB contiguously.
+template <int K, int CB>
 __global__ void __launch_bounds__(256) tcq_decode_packed_kernel(const uint32_t* __restrict__ packed, long long n,
-                                                               int codebook, float* __restrict__ dq) {
+                                                               float* __restrict__ dq) {
     constexpr uint32_t NW = Geo<K>::NWORDS;
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one per 4 weights
-    const long long tile = gid >> 6;
+    const long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (tile >= n) return;
-    const uint32_t t0 = uint32_t(gid & 63) * 4;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t sb = (kT - 8 - 8 * lane) * K;            // stream bit of the lane's last weight (t = 8l + 7)
+    const uint32_t word0 = sb >> 5, sh = sb & 31;
     const uint32_t* const p = packed + tile * NW;
-    float o[4];
+    uint32_t v[3];
 #pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-        const uint32_t bit = (kT - 1 - (t0 + i)) * K;
-        const uint32_t j = bit >> 5, sh = bit & 31;
-        const uint32_t w0 = __ldg(p + j);
-        const uint32_t w1 = __ldg(p + (j + 1 == NW ? 0 : j + 1));
-        const uint32_t win = __funnelshift_r(w0, w1, sh);      // (w1:w0) >> sh, low 32 bits
-        o[i] = cb_value_rt(codebook, win & 0xFFFFu);
+    for (uint32_t j = 0; j < 3; ++j) {
+        const uint32_t wi = word0 + j;
+        v[j] = __ldg(p + (wi >= NW ? wi - NW : wi));         // lane 0's windows wrap to word 0
     }
-    *reinterpret_cast<float4*>(dq + tile * kT + t0) = make_float4(o[0], o[1], o[2], o[3]);
+    const uint32_t u0 = __funnelshift_r(v[0], v[1], sh), u1 = __funnelshift_r(v[1], v[2], sh);
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        constexpr int kMaxOff = 7 * K;                       // 28 at most: the window starts inside u0
+        const int s = (7 - i) * K;
+        static_assert(kMaxOff < 32, "window offsets must start in the first normalised word");
+        const uint32_t win = (s + 16 <= 32) ? (u0 >> s) : __funnelshift_r(u0, u1, s);
+        o[i] = cb_value<CB>(win & 0xFFFFu);
+    }
+    float4* const out = reinterpret_cast<float4*>(dq + tile * kT + 8 * lane);
+    out[0] = make_float4(o[0], o[1], o[2], o[3]);
+    out[1] = make_float4(o[4], o[5], o[6], o[7]);
 }
 
 // Symbol-stream decode (decode_recursive == decode_window, qtip.py:70-110).
@@ -82,16 +93,28 @@ __global__ void __launch_bounds__(256) tcq_codebook_lut_kernel(int codebook, flo
 
 }  // namespace
 
-cudaError_t launch_decode_packed(const uint32_t* packed, long long n, int K, int codebook, float* dq, cudaStream_t stream) {
-    if (n <= 0) return cudaSuccess;
-    const unsigned grid = unsigned((n * 64 + 255) / 256);
-    switch (K) {
-        case 2: tcq_decode_packed_kernel<2><<<grid, 256, 0, stream>>>(packed, n, codebook, dq); break;
-        case 3: tcq_decode_packed_kernel<3><<<grid, 256, 0, stream>>>(packed, n, codebook, dq); break;
-        case 4: tcq_decode_packed_kernel<4><<<grid, 256, 0, stream>>>(packed, n, codebook, dq); break;
+namespace {
+template <int K>
+cudaError_t launch_decode_packed_k(const uint32_t* packed, long long n, int codebook, float* dq, cudaStream_t stream) {
+    const unsigned grid = unsigned((n + 7) / 8);
+    switch (codebook) {
+        case kCb1Mad:  tcq_decode_packed_kernel<K, kCb1Mad><<<grid, 256, 0, stream>>>(packed, n, dq); break;
+        case kCb3Inst: tcq_decode_packed_kernel<K, kCb3Inst><<<grid, 256, 0, stream>>>(packed, n, dq); break;
+        case kCbMcg:   tcq_decode_packed_kernel<K, kCbMcg><<<grid, 256, 0, stream>>>(packed, n, dq); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t launch_decode_packed(const uint32_t* packed, long long n, int K, int codebook, float* dq, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    switch (K) {
+        case 2: return launch_decode_packed_k<2>(packed, n, codebook, dq, stream);
+        case 3: return launch_decode_packed_k<3>(packed, n, codebook, dq, stream);
+        case 4: return launch_decode_packed_k<4>(packed, n, codebook, dq, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t launch_decode_symbols(const long long* bits, long long n, long long T, int K, int codebook,
