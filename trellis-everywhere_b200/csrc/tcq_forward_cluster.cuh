@@ -172,18 +172,20 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
 
     long long tile0 = 0;                           // first tile of the group being processed
 
-    // stream one step's row slices of tile set `s` (written during step t) to HBM (coalesced 128-bit stores)
-    auto flush_set = [&](int s, int t, long long tile0) {
+    // stream one step's row slices of tile set `s` (written during step t into staging buffer `buf` = t & 1) to HBM
+    // (coalesced 128-bit stores).  A set's slices are GS * ROWBC / 16 <= NT words, one per thread; which word, which
+    // tile of the set and the byte offset from the set's first row are fixed for the launch.
+    constexpr int V = ROWBC / 16;
+    static_assert(GS * V <= NT, "one 128-bit word of a set's row slices per thread");
+    const int fl_gg = tid / V;
+    const bool fl_on = tid < GS * V;
+    const size_t fl_off = size_t(fl_gg) * a.bp_steps * ROWB + size_t(rank) * ROWBC + size_t(tid - fl_gg * V) * 16;
+    auto flush_set = [&](int s, int t, int buf, long long tile0) {
         if (t < t_store0) return;
-        const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(t & 1) * G * ROWBC + size_t(s) * GS * ROWBC);
-        constexpr int V = ROWBC / 16;
-        for (int i = tid; i < GS * V; i += NT) {
-            const int gg = i / V, cc = i - gg * V;
-            const long long tile = tile0 + s * GS + gg;
-            if (tile < a.n) {
-                uint4* d = reinterpret_cast<uint4*>(a.bp + (size_t(tile) * a.bp_steps + (t - t_store0)) * ROWB + size_t(rank) * ROWBC);
-                d[cc] = src[i];
-            }
+        if (fl_on && tile0 + s * GS + fl_gg < a.n) {
+            const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(buf) * G * ROWBC + size_t(s) * GS * ROWBC);
+            unsigned char* row0 = a.bp + (size_t(tile0 + s * GS) * a.bp_steps + (t - t_store0)) * ROWB;     // uniform
+            *reinterpret_cast<uint4*>(row0 + fl_off) = src[tid];
         }
     };
 
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
             const float wt = wv[(s * GS + gg) * kT + ((t + a.roll) & (kT - 1))];
             w2[gg] = pack2(wt, wt);
         }
-        unsigned char* const st = stage + size_t(t & 1) * G * ROWBC;
+        unsigned char* const st = stage + size_t(cur) * G * ROWBC;        // cur == t & 1
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
 #pragma unroll
@@ -242,7 +244,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
                 const uint32_t m = dst_bar[i] + uint32_t(2 * s + (cur ^ 1)) * 8u;
 #pragma unroll
                 for (int lu = 0; lu < LU; ++lu) {
-                    if (i == NI / 2 && gg == GS / 2 && lu == ((NI > 1 || GS > 1) ? 0 : LU / 2) && t > 0) flush_set(s, t - 1, tile0);
+                    if (i == NI / 2 && gg == GS / 2 && lu == ((NI > 1 || GS > 1) ? 0 : LU / 2) && t > 0) flush_set(s, t - 1, cur ^ 1, tile0);
                     float c[Q];
 #pragma unroll
                     for (int j = 0; j < Q / 2; ++j)
@@ -327,10 +329,13 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
 
         // The two tile sets alternate; every step_set waits for its input buffer's bytes, computes,
         // waits for the previous step_set's barrier phase before its first store, stores, arrives.
+        // (two steps per trip, so that the buffer index is a constant in every instance of step_set)
         step_set(0, 0, 0);
-        for (int t = 0; t < kT; ++t) {
-            step_set(1, t, t & 1);
-            if (t + 1 < kT) step_set(0, t + 1, (t + 1) & 1);
+        for (int t = 0; t < kT; t += 2) {
+            step_set(1, t, 0);
+            step_set(0, t + 1, 1);
+            step_set(1, t + 1, 1);
+            if (t + 2 < kT) step_set(0, t + 2, 0);
         }
         cluster_wait_relaxed();          // closes the phase opened by the last step_set
         wait_pending = false;
@@ -339,8 +344,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         // The barrier phase above was entered at the START of the last step_set, so it says nothing
         // about that step's backpointer bytes; the rows are CTA-local, a CTA barrier orders them.
         __syncthreads();
-        flush_set(0, kT - 1, tile0);
-        flush_set(1, kT - 1, tile0);
+        flush_set(0, kT - 1, (kT - 1) & 1, tile0);
+        flush_set(1, kT - 1, (kT - 1) & 1, tile0);
 
         // ---- final metrics live in buffer 0 (256 steps), layout [Q][HNC] = edges q*HN + rank*HNC + hl ----
         const int fin = 0;
