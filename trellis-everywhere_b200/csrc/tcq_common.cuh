@@ -163,8 +163,12 @@ template <> __device__ __forceinline__ float min_of<16>(const float (&c)[16]) {
 __device__ __forceinline__ void take_if_equal_fma(float& tag, float c, float best, float zero, float value) {
     asm("{\n\t.reg .pred p;\n\tsetp.eq.f32 p, %1, %2;\n\t@p fma.rn.f32 %0, %1, %3, %4;\n\t}" : "+f"(tag) : "f"(c), "f"(best), "f"(zero), "f"(value));
 }
+// Q = candidates per successor.  With 8 or fewer, every other move is a select; with 16 the compare/select
+// pipe is the busier one and only every fourth move stays there (measured: +1.4 % at K = 4, -0.5 % at K = 3).
+template <int Q>
 __device__ __forceinline__ void take_if_equal_balanced(int q, float& tag, float c, float best, float zero, float value) {
-    if (q & 1) tag = (c == best) ? value : tag;
+    const bool on_select_pipe = Q >= 16 ? (q & 3) == 1 : (q & 1) != 0;
+    if (on_select_pipe) tag = (c == best) ? value : tag;
     else take_if_equal_fma(tag, c, best, zero, value);
 }
 

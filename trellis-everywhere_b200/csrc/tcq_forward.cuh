@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
                         // lowest q whose candidate equals the minimum (== first minimum, as torch.min)
                         float tag = float((Q - 1) << (lu * K));
 #pragma unroll
-                        for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced(q, tag, c[q], best, zero, float(q << (lu * K)));
+                        for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced<Q>(q, tag, c[q], best, zero, float(q << (lu * K)));
                         outv[g][lu] = best;
                         tags[g] = __fadd_rn(tags[g], tag);
                     }

@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
                     const float best = min_of<Q>(c);
                     float tag = float((Q - 1) << (lu * K));
 #pragma unroll
-                    for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced(q, tag, c[q], best, zero, float(q << (lu * K)));
+                    for (int q = Q - 2; q >= 0; --q) take_if_equal_balanced<Q>(q, tag, c[q], best, zero, float(q << (lu * K)));
                     outv[lu % SV] = best;
                     tags = __fadd_rn(tags, tag);
                     if (i == NI - 1 && gg == GS - 1 && lu == 0) {
