@@ -117,6 +117,15 @@ def make_tiles(torch, qtip, device, seed: int):
     return ip.tiles
 
 
+def host_threads() -> int:
+    """Cores this process may run on.  Not the OpenMP default: torchrun exports OMP_NUM_THREADS=1 to every rank, which
+    would make the CPU legs single-threaded whenever the benchmark is launched for more than one GPU."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_port_rate(tiles_np, seconds: float, threads: int):
     """Weights/s of the CPU oracle on a bounded sample of `tiles_np`, sized to take about `seconds`."""
     from oracle import oracle as O
@@ -141,7 +150,7 @@ def run_reference(args, rank: int, world: int) -> None:
     import numpy as np
     from oracle import oracle as O
     O.build()
-    threads = O.max_threads()
+    threads = host_threads()
     rng = np.random.default_rng(0)
     # same distribution as the incoherence-processed tiles: ~N(0, 1.2437^2)
     sample = max(threads, (args.ref_tiles // threads) * threads)
@@ -296,7 +305,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as O
             O.build()
-            threads = O.max_threads()
+            threads = host_threads()
             rate, n_s, dt = cpu_port_rate(tiles[:4096].cpu().numpy(), args.cpu_seconds, threads)
             cpu = {"value": rate, "unit": "weights/s", "cores": threads, "kind": "port",
                    "sample": f"first {n_s} tiles of the same workload, {dt:.1f} s"}
