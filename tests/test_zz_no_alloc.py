@@ -1,7 +1,6 @@
 """tcq_encode_tb_static: the encoder for callers that cannot allocate device memory.
 
-A host that has handed its whole device budget to another framework, or that is inside a
-stream capture, cannot produce the workspace tcq_encode_tb wants.  The static entry point keeps
+A host that has handed its whole device budget to another framework cannot produce the workspace tcq_encode_tb wants.  The static entry point keeps
 its scratch in a fixed array of the library image instead.  It must give exactly what the
 ordinary entry point gives, call after call (the array is reused and never cleared), and must
 refuse batches that do not fit.

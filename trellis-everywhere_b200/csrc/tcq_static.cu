@@ -1,8 +1,8 @@
 // tcq_encode_tb_static: the tail-biting encoder for callers that cannot allocate device memory.
 //
 // Some hosts of this library may not call cudaMalloc at the point where they need the encoder:
-// a plugin running inside another framework's memory budget, code between cudaStreamBeginCapture
-// and EndCapture, a service that fixed its device footprint at start-up.  tcq_encode_tb asks such a
+// a plugin running inside another framework's memory budget, a service that fixed its device
+// footprint at start-up.  tcq_encode_tb asks such a
 // caller for a workspace it has no way to obtain.  This entry point needs none: the backpointer
 // scratch is a fixed array in the library's own device image.
 //
