@@ -110,7 +110,7 @@ bool misaligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p)
 
 extern "C" {
 
-int tcq_abi_version(void) { return 2; }
+int tcq_abi_version(void) { return 3; }
 
 const char* tcq_strerror(int code) {
     switch (code) {
