@@ -181,3 +181,25 @@ def test_ldlq_row_groups_side_by_side(mods, golden):
     assert abs(obj(w3) - obj(w1)) <= 0.02 * obj(w1)
     ld = l.tcq_quantize_weight_ldlq(w, K=3, lut="mcg", H=H, seed=0, row_groups=2)
     assert abs(obj(ld) - obj(w1)) <= 0.02 * obj(w1)
+
+
+def test_model_encode_writes_loadable_shards(mods, tmp_path):
+    """encode_model(shard_dir=...) leaves one shard per matrix in the exporter's format; the merged manifest and the
+    files alone reproduce y = W_hat x (up to the fp16 rounding of the stored scale vectors)."""
+    q, _ = mods
+    from trellis_b200 import model, shards
+    shapes = {"model.layers.0.self_attn.k_proj": (32, 128), "model.layers.0.mlp.down_proj": (64, 128)}
+    hess = lambda name, k, dev: model.synthetic_hessian(name, k, dev, rows=512)
+    model.encode_model(shapes, K=3, codebook="mcg", hessian_fn=hess, shard_dir=str(tmp_path), streams=2)
+    man = shards.merge_manifest(str(tmp_path))
+    for name, (n, k) in shapes.items():
+        rec = shards.read_quant(str(tmp_path), man, name + ".weight")
+        assert rec["n_out"] == n and rec["k_in"] == k and rec["K"] == 3 and rec["shard"] == name + ".bin"
+        w = model.synthetic_weight(name, (n, k), torch.device("cuda"))
+        H = hess(name, k, w.device) if model.is_mlp(name) else None
+        packed, w_hat, _ = model.encode_matrix(w, 3, "mcg", model.seed_of(name), H)
+        assert np.array_equal(rec["bits"], packed.cpu().numpy().view(np.uint32))
+        x = torch.randn(k, generator=torch.Generator().manual_seed(1)).cuda()
+        y = shards.packed_linear(rec, x)
+        want = w_hat @ x
+        assert float((y - want).norm() / want.norm()) < 2e-3

@@ -31,6 +31,7 @@ import torch.distributed as dist
 from . import dist as tdist
 from . import ldlq as tldlq
 from . import qtip
+from . import shards
 
 
 _linalg_lock = threading.Lock()
@@ -80,7 +81,7 @@ def synthetic_hessian(name: str, k: int, device, rows: int = 8192) -> torch.Tens
 
 @torch.no_grad()
 def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torch.Tensor] = None,
-                  sigma_reg: float = 0.025, row_groups: int = 1):
+                  sigma_reg: float = 0.025, row_groups: int = 1, return_ip: bool = False):
     """One matrix: returns (packed int32 [n_tiles, 8K] in the reference's tile order, W_hat, relative error).
 
     Plain: tiles ordered ``(row/16) * (k/16) + col/16`` (qtip.py:288).  LDLQ: the same order, assembled from the
@@ -116,17 +117,21 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
         packed = store.reshape(-1, nw)
         w_hat = ip.restore(zq)
     rel = float(((w - w_hat) ** 2).mean() / w.square().mean())
+    if return_ip:                          # the sign and scale vectors a shard needs next to the packed words
+        return packed, w_hat, rel, ip
     return packed, w_hat, rel
 
 
 def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg", ldlq_filter: Callable[[str], bool] = is_mlp,
                  weight_fn: Callable = synthetic_weight, hessian_fn: Optional[Callable] = synthetic_hessian,
                  out_dir: Optional[str] = None, device=None, group=None, gather: bool = True,
-                 log: Optional[Callable[[dict], None]] = None, streams: int = 1):
+                 log: Optional[Callable[[dict], None]] = None, streams: int = 1, shard_dir: Optional[str] = None):
     """Encode this rank's share of the model; returns (results of this rank, gathered packed words on rank 0).
 
     ``results``: name -> {"tiles", "seconds", "weights_per_s", "rel_err", "ldlq", "skipped"}.
     ``streams`` > 1 keeps that many matrices in flight on this GPU (one host thread + CUDA stream each).
+    ``shard_dir``: every finished matrix is also written as a packed-model shard ``<name>.bin`` + ``.bin.json`` in the
+    reference exporter's format (``shards.Shard``); ``shards.merge_manifest(shard_dir)`` then builds ``manifest.json``.
     Works without an initialised process group (single process = rank 0 of 1).
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -137,6 +142,8 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
     results, packed_out = {}, {}
     if out_dir:
         os.makedirs(out_dir, exist_ok=True)
+    if shard_dir:
+        os.makedirs(shard_dir, exist_ok=True)
 
     def one(name: str, stream) -> None:
         n_out, k_in = shapes[name]
@@ -150,9 +157,13 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
         H = hessian_fn(name, k_in, dev) if use_ldlq else None
         stream.synchronize()
         t0 = time.perf_counter()
-        packed, _, rel = encode_matrix(w, K, codebook, seed_of(name), H)
+        packed, _, rel, ip = encode_matrix(w, K, codebook, seed_of(name), H, return_ip=True)
         stream.synchronize()
         dt = time.perf_counter() - t0
+        if shard_dir:
+            sh = shards.Shard(os.path.join(shard_dir, name + ".bin"))
+            sh.put_quant(name + ".weight", packed, ip, n_out, k_in, K)
+            sh.flush()
         rec = {"name": name, "rank": rank, "gpu": dev.index, "tiles": packed.shape[0], "seconds": dt,
                "weights_per_s": n_out * k_in / dt, "rel_err": rel, "ldlq": use_ldlq, "skipped": False}
         results[name] = rec
@@ -250,6 +261,7 @@ def main(argv=None) -> None:
     ap.add_argument("--no-ldlq", action="store_true", help="plain TCQ everywhere (the reference's Hessian-free mode)")
     ap.add_argument("--hessian-rows", type=int, default=8192)
     ap.add_argument("--streams", type=int, default=3, help="matrices in flight per GPU (1 = one after another)")
+    ap.add_argument("--shards", default=None, help="folder for packed-model shards in the reference exporter's format")
     ap.add_argument("--out", default=None, help="folder for <name>.bits.npy files and per-rank JSONL logs (enables resume)")
     args = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -273,7 +285,7 @@ def main(argv=None) -> None:
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
     results, gathered = encode_model(shapes, args.K, args.codebook, hessian_fn=hess, out_dir=args.out, device=dev, log=log,
-                                     streams=args.streams)
+                                     streams=args.streams, shard_dir=args.shards)
     torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
