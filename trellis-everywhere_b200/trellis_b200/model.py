@@ -38,9 +38,16 @@ _linalg_lock = threading.Lock()
 
 
 def qwen3_8b_shapes(layers: int = 36, hidden: int = 4096, inter: int = 12288, q_heads: int = 32, kv_heads: int = 8,
-                    head_dim: int = 128) -> Dict[str, Tuple[int, int]]:
-    """``name -> (n_out, k_in)`` of the linears ``apply_tcq`` walks in a Qwen3-8B-shaped model (252 matrices)."""
+                    head_dim: int = 128, embeddings: bool = False, vocab: int = 151936) -> Dict[str, Tuple[int, int]]:
+    """``name -> (n_out, k_in)`` of the linears ``apply_tcq`` walks in a Qwen3-8B-shaped model (252 matrices).
+
+    ``embeddings`` adds the two ``[vocab, hidden]`` matrices that the reference's exporter also packs
+    (``export_packed_8b.py:221-253``) and that ``apply_tcq`` skips because they are not ``nn.Linear``.
+    """
     shapes = {}
+    if embeddings:
+        shapes["model.embed_tokens"] = (vocab, hidden)
+        shapes["lm_head"] = (vocab, hidden)
     for i in range(layers):
         p = f"model.layers.{i}."
         shapes[p + "self_attn.q_proj"] = (q_heads * head_dim, hidden)
@@ -258,6 +265,7 @@ def main(argv=None) -> None:
     ap.add_argument("--inter", type=int, default=12288)
     ap.add_argument("--K", type=int, default=3)
     ap.add_argument("--codebook", default="mcg")
+    ap.add_argument("--with-embeddings", action="store_true", help="also encode embed_tokens and lm_head ([151936, hidden])")
     ap.add_argument("--no-ldlq", action="store_true", help="plain TCQ everywhere (the reference's Hessian-free mode)")
     ap.add_argument("--hessian-rows", type=int, default=8192)
     ap.add_argument("--streams", type=int, default=3, help="matrices in flight per GPU (1 = one after another)")
@@ -271,7 +279,8 @@ def main(argv=None) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     rank = dist.get_rank() if world > 1 else 0
-    shapes = qwen3_8b_shapes(args.layers, args.hidden, args.inter, q_heads=args.hidden // 128, kv_heads=max(1, args.hidden // 512))
+    shapes = qwen3_8b_shapes(args.layers, args.hidden, args.inter, q_heads=args.hidden // 128, kv_heads=max(1, args.hidden // 512),
+                             embeddings=args.with_embeddings)
     logf = open(os.path.join(args.out, f"rank{rank}.jsonl"), "a") if args.out and (os.makedirs(args.out, exist_ok=True) or True) else None
 
     def log(rec):
