@@ -275,3 +275,20 @@ def _mcg_rms() -> float:
     hi = (r >> np.uint32(16)).astype(np.uint16).view(np.float16).astype(np.float32)
     lo = (r & np.uint32(0xFFFF)).astype(np.uint16).view(np.float16).astype(np.float32)
     return float(torch.from_numpy(hi + lo).square().mean().sqrt().item())
+
+
+def test_model_shapes_match_the_fifth_configuration():
+    """252 linears / 6 945 767 424 weights / 27 131 904 tiles of the Qwen3-8B shape that the reference's loop walks
+    (scripts/run_tcq_eval.py:106-127), plus the two embedding-sized matrices its exporter packs on request."""
+    from trellis_b200 import model
+    shapes = model.qwen3_8b_shapes()
+    assert len(shapes) == 252
+    assert sum(n * k for n, k in shapes.values()) == 6_945_767_424
+    assert sum((n // 16) * (k // 16) for n, k in shapes.values()) == 27_131_904
+    assert sum(model.is_mlp(n) for n in shapes) == 108
+    more = model.qwen3_8b_shapes(embeddings=True)
+    assert len(more) == 254 and more["lm_head"] == (151936, 4096) == more["model.embed_tokens"]
+    plan = tdist.model_plan(more, [n for n in more if model.is_mlp(n)], 8)
+    assert sorted(n for p in plan for n in p) == sorted(more)
+    assert {plan[0][0], plan[1][0]} == {"lm_head", "model.embed_tokens"}        # the two largest go first, on different ranks
+    assert model.seed_of("model.layers.0.mlp.up_proj") == __import__("zlib").crc32(b"model.layers.0.mlp.up_proj")
