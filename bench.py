@@ -181,7 +181,7 @@ def run_reference(args, rank: int, world: int) -> None:
 def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
-    from trellis_b200 import _lib, dist as tdist, qtip
+    from trellis_b200 import _lib, qtip
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the B200 encoder has no CPU fallback")

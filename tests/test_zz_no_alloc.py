@@ -8,7 +8,6 @@ refuse batches that do not fit.
 Collected last on purpose (file name), so a run that stops at the first failure has already
 gone through every other test.
 """
-import numpy as np
 import pytest
 import torch
 
