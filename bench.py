@@ -4,14 +4,23 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
 One step = one pass of the hot path over one batch: the tiles of one 4096 x 4096 matrix
-(iid N(0, 0.02^2) with 1 % outliers x20) after randomized-Hadamard incoherence processing,
-i.e. 65 536 independent 256-weight tiles, encoded at K = 3 with the 3INST codebook (packed
-codes, reconstruction and per-tile squared error out).  The matrix is synthetic: seeded
-random values with the shape and distribution the reference's real weights would have.
+(iid N(0, 0.02^2) with 1 % outliers x20, CPU generator seed 0) after randomized-Hadamard
+incoherence processing with seed 0, i.e. 65 536 independent 256-weight tiles, encoded at
+K = 3 with the 3INST codebook (packed codes, reconstruction and per-tile squared error out).
+The matrix is synthetic: seeded random values with the shape and distribution the reference's
+real weights would have; it is built on the host exactly as the configuration states it
+(``trellis_b200.workloads.cfg2_tiles``), so the tiles, and ``mse_z``, are the same on every box.
 
-With N > 1 (launched by torchrun, one rank per GPU) every rank encodes its own matrix of
-the same shape (weak scaling: work shards by whole matrices, no exchange during compute)
-and the packed codes are gathered to rank 0 over NCCL inside the timed step.
+With N > 1 (launched by torchrun, one rank per GPU) every rank encodes a matrix of that
+shape (weak scaling: work shards by whole matrices, no exchange during compute) and the
+packed codes are gathered over NCCL inside the timed step.  After the timed region two
+further multi-GPU measurements are taken once each and added to the line:
+  tile_split    ONE such matrix cut into contiguous tile ranges over the N ranks, packed
+                codes all-gathered (strong scaling of a single plain matrix);
+  model_encode  a fixed slice of the Qwen3-8B-shaped model (8 of 36 layers = 56 matrices,
+                1.54 G weights, LDLQ with synthetic Hessians on the 24 MLP matrices), whole
+                matrices placed longest-first on the ranks, three matrices in flight per GPU,
+                packed codes gathered to rank 0 (strong scaling of the model-level encode).
 
 Printed: ONE JSON line on rank 0 with
   value     whole-job weights/s with the tiles resident in HBM, timed with CUDA events
@@ -21,9 +30,14 @@ Printed: ONE JSON line on rank 0 with
   roofline  the Viterbi step kernel alone, timed live with CUDA events through the
             forward-only entry point, against the fp32/INT lane-issue ceiling;
   cpu_baseline  the CPU oracle (a C port of the reference's PyTorch dynamic programme)
-            on a bounded sample of the same tiles, all host threads (N = 1 only).
+            on a bounded sample of the same tiles, all host threads (N = 1 only);
+  parity    64 tiles spread over the last timed step's output and 64 tiles of the launches the
+            roofline leg times, checked bit for bit against the CPU oracle after the timing.
 
-``--impl reference`` times that CPU port alone (rank 0 only) and prints the same kind of line.
+``--impl reference`` times the reference's own ``viterbi_tb`` (fp32 PyTorch DP, the staged copy under
+``oracle/_ref``) on the host cores, rank 0 only, on tiles of the same workload, and prints the same kind of
+line with the C port's rate beside it; without the staged copy it times the C port.
+``--impl reference-triton`` (never the default; one GPU) times the reference's Triton encoder on the GPU.
 """
 from __future__ import annotations
 
@@ -105,16 +119,10 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
-def make_tiles(torch, qtip, device, seed: int):
-    """The second benchmark configuration's tiles, generated on the device: [65536, 256] fp32."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    n, k = MATRIX
-    w = torch.randn(n, k, generator=g, device=device) * 0.02
-    mask = torch.rand(n, k, generator=g, device=device) < 0.01
-    w = torch.where(mask, w * 20, w)
-    lut = qtip.codebook_lut(CODEBOOK, device)
-    ip = qtip.IPContext(w, lut.square().mean().sqrt().item(), seed=0)
-    return ip.tiles
+def workload_tiles_host(lut_cpu):
+    """The second benchmark configuration's tiles, built on the host as the configuration states: [65536, 256] fp32."""
+    from trellis_b200 import workloads
+    return workloads.cfg2_tiles(lut_cpu)
 
 
 def host_threads() -> int:
@@ -142,46 +150,231 @@ def cpu_port_rate(tiles_np, seconds: float, threads: int):
     return n * T_SEQ / dt, n, dt
 
 
-# ------------------------------------------------------------------------------------ reference arm
+# ------------------------------------------------------------------------------------ reference arms
 def run_reference(args, rank: int, world: int) -> None:
-    """The reference's CPU implementation of the path (C port, all host threads), rank 0 only."""
+    """The reference's CPU implementation of the path on the box's host cores, rank 0 only.
+
+    With the staged reference (``oracle/_ref``): its own ``viterbi_tb(w, K, lut, dp_dtype=float32)``, all host threads,
+    one batch of the workload's tiles per step at the batch size (16 / 64 / 256 tiles) that the warm-up found fastest
+    and that keeps the run within a few minutes; the C port's rate on the same tiles is reported beside it.
+    """
     if rank != 0:
         return
     import numpy as np
+    import torch
+    from oracle import make_ref
     from oracle import oracle as O
     O.build()
     threads = host_threads()
-    rng = np.random.default_rng(0)
-    # same distribution as the incoherence-processed tiles: ~N(0, 1.2437^2)
-    sample = max(threads, (args.ref_tiles // threads) * threads)
-    tiles = (rng.standard_normal((sample, T_SEQ)) * 1.2437).astype(np.float32)
-    lut = O.codebook_lut(CODEBOOK)
-    for _ in range(args.warmup):
-        O.viterbi_tb(tiles[:threads], K_BITS, lut, nthreads=threads)
+    torch.set_num_threads(threads)
+    lut_np = O.codebook_lut(CODEBOOK)
+    tiles = workload_tiles_host(torch.from_numpy(lut_np))
+    port_rate, port_n, port_dt = cpu_port_rate(tiles[:4096].numpy(), min(args.cpu_seconds, 8.0), threads)
+    port = {"value": port_rate, "unit": "weights/s", "cores": threads, "kind": "port",
+            "sample": f"first {port_n} tiles of the same workload, {port_dt:.1f} s (C/OpenMP restatement of the same DP)"}
+    if make_ref.staged() is not None:
+        rq, _ = make_ref.import_reference()
+        lut = rq.codebook_lut(CODEBOOK)
+        assert np.array_equal(lut.numpy().view(np.uint32), lut_np.view(np.uint32))
+        rates = {}
+        for b in (16, 64, 256):                              # warm-up doubles as the batch-size probe
+            t0 = time.perf_counter()
+            rq.viterbi_tb(tiles[:b], K_BITS, lut, dp_dtype=torch.float32)
+            rates[b] = (b * T_SEQ / (time.perf_counter() - t0), time.perf_counter() - t0)
+        fits = {b: r for b, (r, dt) in rates.items() if dt * (args.steps + args.warmup) <= 150.0} or {16: rates[16][0]}
+        batch = max(fits, key=fits.get)
+        kind, what = "reference", "the reference's own viterbi_tb (fp32 PyTorch DP)"
+
+        def step(i):
+            lo = (i * batch) % (tiles.shape[0] - batch)
+            rq.viterbi_tb(tiles[lo:lo + batch], K_BITS, lut, dp_dtype=torch.float32)
+        probe = {str(b): r for b, (r, _) in rates.items()}
+    else:
+        batch = max(threads, (args.ref_tiles // threads) * threads)
+        kind, what, probe = "port", "C/OpenMP restatement of the reference's DP (reference modules not staged)", None
+        tiles_np = tiles.numpy()
+
+        def step(i):
+            lo = (i * batch) % (tiles_np.shape[0] - batch)
+            O.viterbi_tb(tiles_np[lo:lo + batch], K_BITS, lut_np, nthreads=threads)
+    for i in range(args.warmup):
+        step(i)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.viterbi_tb(tiles, K_BITS, lut, nthreads=threads)
+    for i in range(args.steps):
+        step(args.warmup + i)
     dt = (time.perf_counter() - t0) / args.steps
-    value = sample * T_SEQ / dt
+    value = batch * T_SEQ / dt
     line = {
-        "impl": "reference", "metric": "weights encoded/sec (L=16, K=3)", "value": value, "unit": "weights/s",
+        "impl": "reference", "metric": f"weights encoded/sec (L=16, K={K_BITS})", "value": value, "unit": "weights/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "K": K_BITS, "codebook": CODEBOOK, "tiles_per_step": sample},
-        "cpu_baseline": {"value": value, "unit": "weights/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample} tiles of the workload's distribution per step (the full 65536 would take "
-                                   f"{65536 * T_SEQ / value / 60:.0f} min)"},
+        "config": {"workload": WORKLOAD, "K": K_BITS, "codebook": CODEBOOK, "tiles_per_step": batch},
+        "cpu_baseline": {"value": value, "unit": "weights/s", "cores": threads, "kind": kind,
+                         "sample": f"{batch} tiles of the workload per step through {what}; the full 65536 would take "
+                                   f"{65536 * T_SEQ / value / 60:.0f} min", "batch_probe_weights_per_s": probe, "port": port},
         "e2e": {"value": value, "unit": "weights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def run_reference_triton(args) -> None:
+    """Side arm, one GPU: the reference's Triton encoder (``viterbi_tb_triton``, MCG only) as Triton JIT-compiles it for
+    this GPU, at 2 048 and 16 384 tiles, K = 2 and 3, next to this library on the same tiles (rates, code agreement, MSE)."""
+    import torch
+    from oracle import make_ref
+    if make_ref.staged() is None:
+        print(json.dumps({"impl": "reference-triton", "unavailable": "reference modules not staged under oracle/_ref"}), flush=True)
+        return
+    rq, _ = make_ref.import_reference()
+    try:
+        from trellis.viterbi_triton import viterbi_tb_triton
+    except Exception as e:                                   # triton missing or unusable on this box
+        print(json.dumps({"impl": "reference-triton", "unavailable": f"cannot import the Triton encoder: {e}"[:200]}), flush=True)
+        return
+    from trellis_b200 import qtip
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    lut = rq.codebook_lut("mcg").to(dev)
+    rows = []
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            out = fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps, out
+
+    with ClockSampler(0) as clocks:
+        for K in (2, 3):
+            for n in (2048, 16384):
+                g = torch.Generator(device=dev).manual_seed(K * 100000 + n)
+                w = torch.randn(n, T_SEQ, generator=g, device=dev) * 1.2437
+                ms_t, (bits_t, dq_t) = timed(lambda: viterbi_tb_triton(w, K, lut), max(1, args.steps // 2))
+                ms_b, r = timed(lambda: qtip.encode(w, K, "mcg", want_bits=True), max(3, args.steps))
+                _, dq_ref = rq.viterbi_tb(w[:64], K, lut, dp_dtype=torch.float32)       # its own fp32 DP, on the GPU
+                rows.append({"K": K, "tiles": n, "triton_ms": ms_t, "triton_weights_per_s": n * T_SEQ / (ms_t * 1e-3),
+                             "b200_ms": ms_b, "b200_weights_per_s": n * T_SEQ / (ms_b * 1e-3), "speedup": ms_t / ms_b,
+                             "symbols_equal_frac": float((bits_t == r.bits).float().mean()),
+                             "mse_triton": float(((w - dq_t) ** 2).mean()), "mse_b200": float(((w - r.dq) ** 2).mean()),
+                             "b200_equals_reference_fp32_dp_on_64_tiles": bool(torch.equal(r.dq[:64], dq_ref)),
+                             "triton_equals_reference_fp32_dp_on_64_tiles": bool(torch.equal(dq_t[:64], dq_ref))})
+    head = rows[-1]
+    print(json.dumps({"impl": "reference-triton", "metric": "weights encoded/sec (L=16, K=3)", "value": head["triton_weights_per_s"],
+                      "unit": "weights/s", "n_gpus": 1, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "SIDE ARM: the reference's viterbi_tb_triton (MCG) vs this library on N(0, 1.2437^2) tiles"},
+                      "cases": rows, "clocks": clocks.summary()}), flush=True)
+
+
 # ------------------------------------------------------------------------------------ B200 arm
+def check_parity(torch, qtip, lib, _lib, tiles, last, dev, cid) -> dict:
+    """After the timing: the last timed step's output and the roofline leg's launches against the CPU oracle."""
+    import numpy as np
+    from oracle import oracle as O
+    O.build()
+    lut = O.codebook_lut(CODEBOOK)
+    n = tiles.shape[0]
+    idx = torch.linspace(0, n - 1, min(64, n), device=dev).round().long()
+    w_np = tiles[idx].cpu().numpy()
+    bits, dq, sse = O.viterbi_tb(w_np, K_BITS, lut, with_sse=True)
+    ok_packed = np.array_equal(last.packed[idx].cpu().numpy().view(np.uint32), O.pack_bits(bits, K_BITS))
+    ok_dq = np.array_equal(last.dq[idx].cpu().numpy().view(np.uint32), dq.view(np.uint32))
+    ok_sse = np.array_equal(last.sse[idx].cpu().numpy().view(np.uint32), sse.view(np.uint32))
+    # the launches the roofline leg times: one full chunk through the pass-level entry point (same launch code and
+    # tile-group shape as tcq_forward_pass), states of 64 spread tiles against the oracle's passes
+    chunk = min(n, 24 * torch.cuda.get_device_properties(dev).multi_processor_count)
+    s1 = qtip.viterbi_pass_b200(tiles[:chunk], K_BITS, None, cid, roll=128)
+    jdx = torch.linspace(0, chunk - 1, min(64, chunk), device=dev).round().long()
+    w2 = tiles[:chunk][jdx].cpu().numpy()
+    o1 = O.viterbi_pass(np.roll(w2, 128, axis=1), K_BITS, lut, None)
+    ok_p1 = np.array_equal(s1[jdx].cpu().numpy(), o1)
+    ov = (s1[:, 128] >> K_BITS).to(torch.int32)
+    s2 = qtip.viterbi_pass_b200(tiles[:chunk], K_BITS, ov, cid)
+    o2 = O.viterbi_pass(w2, K_BITS, lut, (o1[:, 128] >> K_BITS).astype(np.int32))
+    ok_p2 = np.array_equal(s2[jdx].cpu().numpy(), o2)
+    return {"tiles": int(idx.numel()), "bits_equal": bool(ok_packed), "dq_equal": bool(ok_dq), "sse_equal": bool(ok_sse),
+            "pass_tiles": int(jdx.numel()), "pass1_states_equal": bool(ok_p1), "pass2_states_equal": bool(ok_p2),
+            "against": "CPU oracle (oracle/tcq_oracle.c), bit for bit"}
+
+
+def measure_tile_split(torch, dist, qtip, tdist, tiles, world: int, rank: int, dev, cid, fence, reps: int = 3) -> dict:
+    """ONE matrix of the workload cut into contiguous tile ranges over the ranks; packed codes all-gathered."""
+    n = tiles.shape[0]
+    lo, hi = tdist.tile_range(n, rank, world)
+    mine = tiles[lo:hi].contiguous()
+
+    def once():
+        r = qtip.encode(mine, K_BITS, cid, want_dq=True, want_sse=True)
+        return tdist.gather_packed(r.packed, n) if world > 1 else r.packed
+
+    once()
+    fence()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        out = once()
+    b.record()
+    fence()
+    t = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    per_round = (sms // 2) * 6                                # tiles one round of 2-SM clusters advances at K = 3
+    return {"what": "one 65536-tile matrix split by contiguous tile ranges, all-gather of packed codes (strong scaling)",
+            "ms": ms, "weights_per_s": n * T_SEQ / (ms * 1e-3), "tiles_per_rank": hi - lo,
+            "rounds_per_rank": (hi - lo) / per_round, "whole_rounds_per_rank": -(-(hi - lo) // per_round),
+            "gathered_rows": int(out.shape[0])}
+
+
+def measure_model_encode(torch, dist, args, world: int, rank: int, dev) -> dict:
+    """A fixed slice of the Qwen3-8B-shaped model through ``model.encode_model`` (strong scaling over the ranks)."""
+    from trellis_b200 import model
+    shapes = model.qwen3_8b_shapes(layers=args.model_layers)
+    recs = []
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    results, gathered = model.encode_model(shapes, K_BITS, "mcg", device=dev, log=recs.append, streams=args.model_streams)
+    torch.cuda.synchronize(dev)
+    busy = time.perf_counter() - t0                           # this rank: its matrices + its part of the gather
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    ldlq_s = sum(r["seconds"] for r in recs if r["ldlq"])
+    plain_s = sum(r["seconds"] for r in recs if not r["ldlq"])
+    stats = torch.tensor([busy, ldlq_s, plain_s, float(len(recs))], dtype=torch.float64, device=dev)
+    if world > 1:
+        allst = [torch.empty_like(stats) for _ in range(world)]
+        dist.all_gather(allst, stats)
+        w_t = torch.tensor([wall], dtype=torch.float64, device=dev)
+        dist.all_reduce(w_t, op=dist.ReduceOp.MAX)
+        wall = float(w_t)
+    else:
+        allst = [stats]
+    total = sum(a * b for a, b in shapes.values())
+    busy_all = [float(x[0]) for x in allst]
+    return {"what": f"{args.model_layers} of 36 Qwen3-8B-shaped layers ({len(shapes)} matrices, {total} weights), K={K_BITS} MCG, "
+                    f"LDLQ (synthetic Hessians from 8192 rows) on the MLP matrices, {args.model_streams} matrices in flight per GPU, "
+                    "whole matrices placed longest-first, packed codes gathered to rank 0; includes weight and Hessian synthesis",
+            "seconds": wall, "weights_per_s": total / wall, "matrices": len(shapes), "weights": total,
+            "rank_busy_seconds": busy_all, "imbalance_max_over_mean": max(busy_all) / (sum(busy_all) / len(busy_all)),
+            "matrix_seconds_ldlq": [float(x[1]) for x in allst], "matrix_seconds_plain": [float(x[2]) for x in allst],
+            "matrices_per_rank": [int(x[3]) for x in allst],
+            "gathered_matrices": len(gathered) if gathered is not None else 0,
+            "note": "matrix_seconds_* add up the per-matrix times of overlapping matrices, so they exceed the busy time"}
+
+
 def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
     from trellis_b200 import _lib, qtip
+    from trellis_b200 import dist as tdist
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the B200 encoder has no CPU fallback")
@@ -192,9 +385,11 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     lib = _lib.lib()
     cid = qtip.CODEBOOK_IDS[CODEBOOK]
 
-    tiles = make_tiles(torch, qtip, dev, seed=rank)
+    torch.set_num_threads(host_threads())                # torchrun exports OMP_NUM_THREADS=1; the host-side build of the workload is a matmul
+    host = workload_tiles_host(qtip.codebook_lut(CODEBOOK, "cpu")).pin_memory()
     if args.tiles:                                       # reduced case for profiler captures; not the benchmark
-        tiles = tiles[:args.tiles].contiguous()
+        host = host[:args.tiles].contiguous().pin_memory()
+    tiles = host.to(dev)
     n = tiles.shape[0]
     nw = T_SEQ * K_BITS // 32
     gathered = torch.empty((world * n, nw), dtype=torch.int32, device=dev) if world > 1 else None
@@ -226,10 +421,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         e1.record()
         fence()
     ms = e0.elapsed_time(e1)
-    mse = float(last.sse.sum() / tiles.numel())
+    mse = float(last.sse.double().sum() / tiles.numel())
+    qtip.workspace_status(n, K_BITS, dev)                 # raises if a bounded wait gave up or a weight was not finite
 
     # ---- end to end: host tensors through the public API ----
-    host = tiles.cpu().pin_memory()
     h2d = host.numel() * 4
     d2h = n * nw * 4 + n * T_SEQ * 4 + n * 4
     host_out = qtip.Encoded(torch.empty((n, nw), dtype=torch.int32, pin_memory=True),
@@ -266,6 +461,18 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         k1.record()
         torch.cuda.synchronize(dev)
         kern_ms.append(k0.elapsed_time(k1) / reps)
+
+    # ---- parity of what was timed (rank 0 checks its own output; every rank ran the same kernels) ----
+    parity = check_parity(torch, qtip, lib, _lib, tiles, last, dev, cid) if rank == 0 and not args.no_parity else None
+    if parity is not None and not all(v for k, v in parity.items() if k.endswith("_equal")):
+        raise SystemExit(f"parity check against the CPU oracle FAILED: {parity}")
+
+    # ---- the harder multi-GPU shapes, once each ----
+    tile_split = model_enc = None
+    if not args.tiles and not args.no_scaling_extras:
+        tile_split = measure_tile_split(torch, dist, qtip, tdist, tiles, world, rank, dev, cid, fence)
+        qtip.release_workspaces()
+        model_enc = measure_model_encode(torch, dist, args, world, rank, dev)
 
     # ---- reduce over ranks ----
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -306,7 +513,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             from oracle import oracle as O
             O.build()
             threads = host_threads()
-            rate, n_s, dt = cpu_port_rate(tiles[:4096].cpu().numpy(), args.cpu_seconds, threads)
+            rate, n_s, dt = cpu_port_rate(host[:4096].numpy(), args.cpu_seconds, threads)
             cpu = {"value": rate, "unit": "weights/s", "cores": threads, "kind": "port",
                    "sample": f"first {n_s} tiles of the same workload, {dt:.1f} s"}
         line = {
@@ -322,7 +529,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "e2e": {"value": total_weights / (e2e_ms * 1e-3), "unit": "weights/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches_per_step * args.steps,
-            "clocks": ck, "roofline": roofline, "cpu_baseline": cpu, "mse_z": mse,
+            "clocks": ck, "roofline": roofline, "cpu_baseline": cpu, "mse_z": mse, "parity": parity,
+            "tile_split": tile_split, "model_encode": model_enc,
         }
     if world > 1:
         dist.barrier()
@@ -486,7 +694,11 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--impl", choices=("b200", "reference", "reference-triton"), default="b200")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed kernels' output")
+    ap.add_argument("--no-scaling-extras", action="store_true", help="skip the tile_split and model_encode measurements")
+    ap.add_argument("--model-layers", type=int, default=8, help="layers of the Qwen3-8B shape in the model_encode measurement")
+    ap.add_argument("--model-streams", type=int, default=3, help="matrices in flight per GPU in the model_encode measurement")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
     ap.add_argument("--ref-tiles", type=int, default=256, help="tiles per step of the reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -516,6 +728,9 @@ def main() -> None:
             (run_decode_matvec if args.path == "decode_matvec" else run_ip)(args)
     elif args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.impl == "reference-triton":
+        if rank == 0:
+            run_reference_triton(args)
     else:
         if world != args.gpus:
             raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")

@@ -93,6 +93,29 @@ TCQ_API int tcq_encode_tb(const float *w, int64_t n_tiles, int K, int codebook, 
                   float *dq, float *sse, void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * Tail-biting encode of one LDLQ row block, in place in the recursion's own matrices.
+ * Replaces the enc closure of src/trellis/ldlq.py:136-143 (and its bits-capturing twin,
+ * scripts/export_packed_8b.py:117-125): the two transposing copies around the encoder, the
+ * "rows = bW + comp" addition before it (ldlq.py:94) and the "bW - bWq" error after it
+ * (ldlq.py:90,97) are done by the kernels' own loads and stores.
+ *   src     [16][ld] fp32: 16 consecutive input-channel rows of the transposed matrix (k_in x n_out,
+ *           row-major, leading dimension ld >= n_out); n_out a multiple of 16
+ *   comp    [16][ld] fp32 feedback owed to these rows, or NULL; the block encoded is fl(src + comp)
+ *   tile i  = columns 16i .. 16i+15, weight t = (column % 16) * 16 + row   (ldlq.py:138-140)
+ *   packed  code words of tile i at packed + i * packed_stride (u32 units, packed_stride >= 8*K), or NULL;
+ *           with packed_stride = (k_in/16) * 8K and packed pointing at the block's column of the
+ *           [n_out/16][k_in/16][8K] array, the calls of one matrix fill the exporter's tile order directly
+ *   wq      [16][ld] fp32 out: reconstruction in the same layout (required)
+ *   err     [16][ld] fp32 out: src - wq (the uncompensated error the recursion feeds back), or NULL
+ *   sse     [n_out/16] fp32 out: squared error of each tile against src + comp, or NULL
+ *   ws      as tcq_encode_tb, sized for n_out/16 tiles
+ * Codes and reconstruction are bit-identical to tcq_encode_tb on the transposed copy.
+ */
+TCQ_API int tcq_encode_tb_rows(const float *src, const float *comp, int64_t ld, int64_t n_out, int K, int codebook,
+                               uint32_t *packed, int64_t packed_stride, float *wq, float *err, float *sse, void *ws,
+                               size_t ws_bytes, void *stream);
+
+/*
  * One Viterbi pass: the optimal state path of each tile.
  * Replaces _viterbi_pass (src/trellis/qtip.py:147-196) and viterbi_pass_triton
  * (src/trellis/viterbi_triton.py:81-118).
@@ -123,6 +146,12 @@ TCQ_API int tcq_viterbi_pass(const float *w, int64_t n_tiles, int K, int codeboo
 TCQ_API int64_t tcq_encode_tb_static_max_tiles(int K);
 TCQ_API int tcq_encode_tb_static(const float *w, int64_t n_tiles, int K, int codebook, uint32_t *packed, int64_t *bits,
                                  float *dq, float *sse, void *stream);
+/*
+ * tcq_workspace_status for the static-scratch path: health of the LAST tcq_encode_tb_static call on the
+ * current device (TCQ_OK, TCQ_E_DEVICE_TIMEOUT or TCQ_E_NONFINITE_INPUT).  Synchronises the stream and
+ * copies one word to the host; allocates nothing.  No reference counterpart.
+ */
+TCQ_API int tcq_encode_tb_static_status(void *stream);
 
 /*
  * The forward sweep of one pass alone (no traceback): runs the Viterbi step kernel

@@ -30,7 +30,7 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden():
     """name -> numpy archive of the committed outputs of the reference (see tests/golden/make_golden.py)."""
-    return {n: np.load(os.path.join(GOLDEN, n + ".npz")) for n in ("codebooks", "encode", "encode_ip", "decode", "ldlq", "quant", "shard")}
+    return {n: np.load(os.path.join(GOLDEN, n + ".npz")) for n in ("codebooks", "encode", "encode_ip", "cfg2_probe", "decode", "ldlq", "quant", "shard")}
 
 
 @pytest.fixture(scope="session")

@@ -15,7 +15,11 @@ copied here: the outputs are data.
 Files written (all small, committed):
   codebooks.npz   sha256 of the three 65 536-entry fp32 tables + every 251st entry
   encode.npz      torch.manual_seed(0) Gaussian tiles: per codebook x K the pass-1
-                  state path, overlap, pass-2 state path, symbols and reconstruction
+                  state path, overlap, pass-2 state path, symbols and reconstruction (6 tiles),
+                  and the symbols + a digest of the reconstruction for the first 64 tiles
+  cfg2_probe.npz  16 tiles spread over the second benchmark configuration's matrix (4096 x 4096,
+                  CPU generator seed 0, outliers, IPContext(seed=0)) as the reference's own
+                  IPContext produced them, with the reference's symbols (3INST, K=3)
   encode_ip.npz   tiles of an outlier-heavy matrix after incoherence processing
                   (3INST, K=3), the second benchmark configuration in miniature
   decode.npz      decode_recursive / decode_window on random symbols (with and
@@ -136,7 +140,34 @@ def main(ref_root: str, only: str = "") -> None:
             enc[key + "_bits"] = bits.numpy().astype(np.uint8)
             enc[key + "_dq"] = dq.numpy()
             print(key, "mse", float(((w - dq) ** 2).mean()))
+    # the same generator's first 64 tiles: symbols in full, reconstruction as a digest (it follows from the symbols)
+    w64 = w_all[:64].contiguous()
+    enc["w64"] = w64.numpy()
+    for n in names:
+        for K in (2, 3, 4):
+            bits, dq = viterbi_tb(w64, K, luts[n])
+            key = f"{n}_K{K}"
+            assert np.array_equal(bits[:n_tiles].numpy().astype(np.uint8), enc[key + "_bits"])
+            enc[key + "_bits64"] = bits.numpy().astype(np.uint8)
+            enc[key + "_dq64_sha256"] = np.frombuffer(hashlib.sha256(dq.numpy().tobytes()).digest(), dtype=np.uint8)
+            print(key, "64 tiles: sha256(bits)[:16]", hashlib.sha256(bits.numpy().astype(np.uint8).tobytes()).hexdigest()[:16],
+                  "mse", float(((w64 - dq) ** 2).mean()))
     np.savez_compressed(os.path.join(HERE, "encode.npz"), **enc)
+
+    # ---- the second benchmark configuration itself: 16 tiles spread over its 65 536 ----
+    g = torch.Generator().manual_seed(0)
+    m2 = torch.randn(4096, 4096, generator=g) * 0.02
+    mask2 = torch.rand(4096, 4096, generator=g) < 0.01
+    m2 = torch.where(mask2, m2 * 20, m2)
+    lut = luts["3inst"]
+    ip2 = IPContext(m2, lut.square().mean().sqrt().item(), seed=0)
+    tiles2 = ip2.z.view(256, 16, 256, 16).permute(0, 2, 1, 3).reshape(-1, T_SEQ)
+    idx2 = torch.tensor([min(i * 4369, 65535) for i in range(16)])
+    sel2 = tiles2[idx2].contiguous()
+    bits2, dq2 = viterbi_tb(sel2, 3, lut)
+    np.savez_compressed(os.path.join(HERE, "cfg2_probe.npz"), index=idx2.numpy(), tiles=sel2.numpy(),
+                        bits=bits2.numpy().astype(np.uint8), dq=dq2.numpy(),
+                        z_rms=np.float64(ip2.z.square().mean().sqrt().item()), scale=np.float64(ip2.scale))
 
     # ---- encoder: incoherence-processed outlier matrix (3INST, K=3) ----------------
     g = torch.Generator().manual_seed(0)
@@ -173,7 +204,7 @@ def main(ref_root: str, only: str = "") -> None:
     torch.manual_seed(4)
     wq_in = torch.randn(128, 256) * 0.02
     qd = {"w": wq_in.numpy()}
-    for K in (2, 3):
+    for K in (2, 3, 4):
         qd[f"mcg_K{K}_w_hat"] = tcq_quantize_weight(wq_in, K=K, lut=luts["mcg"], seed=0, tile_batch=256,
                                                     dp_dtype=torch.float32, backend="torch").numpy()
     np.savez_compressed(os.path.join(HERE, "quant.npz"), **qd)

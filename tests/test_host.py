@@ -292,3 +292,99 @@ def test_model_shapes_match_the_fifth_configuration():
     assert sorted(n for p in plan for n in p) == sorted(more)
     assert {plan[0][0], plan[1][0]} == {"lm_head", "model.embed_tokens"}        # the two largest go first, on different ranks
     assert model.seed_of("model.layers.0.mlp.up_proj") == __import__("zlib").crc32(b"model.layers.0.mlp.up_proj")
+
+
+def _gloo_leaver_worker(rank, world, port, tmp):
+    """Rank 1 leaves between steps, before the gather; rank 0 must get a clean error within seconds, not hang."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    local = torch.arange(3 * 24, dtype=torch.int32).reshape(3, 24) if rank == 0 else torch.zeros((2, 24), dtype=torch.int32)
+    dist.barrier()                                           # both ranks are up; the rendezvous worked
+    if rank == 1:
+        os._exit(0)                                          # dies with nothing in flight
+    t0 = time.monotonic()
+    try:
+        tdist.gather_packed(local, 5, dst=0)
+        outcome = "returned"
+    except Exception as e:                                   # gloo reports the lost peer or the timeout
+        outcome = "error:" + type(e).__name__
+    open(os.path.join(tmp, "r0"), "w").write(f"{outcome} {time.monotonic() - t0:.1f}")
+    os._exit(0)                                              # the group is broken: no orderly teardown to wait for
+
+
+def test_gather_fails_cleanly_when_a_rank_has_left(tmp_path):
+    """Host-side failure detection of the one collective: a rank that exits before ``gather_packed`` turns into an
+    exception on the surviving rank within the process group's timeout."""
+    port = 33500 + os.getpid() % 2000
+    ctx = mp.start_processes(_gloo_leaver_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False, start_method="spawn")
+    import time
+    deadline = time.monotonic() + 60
+    while not os.path.exists(os.path.join(tmp_path, "r0")) and time.monotonic() < deadline:
+        time.sleep(0.2)
+    for p in ctx.processes:
+        p.join(timeout=10)
+        if p.is_alive():
+            p.kill()
+    outcome, secs = open(os.path.join(tmp_path, "r0")).read().split()
+    assert outcome.startswith("error:"), outcome
+    assert float(secs) < 30
+
+
+def test_second_configuration_tiles_agree_with_the_reference(golden, oracle, luts):
+    """``workloads.cfg2_tiles`` (CPU generator + the host form of incoherence processing) against 16 tiles of the
+    same matrix as the reference's own ``IPContext`` produced them."""
+    from trellis_b200 import workloads
+    g = golden["cfg2_probe"]
+    tiles = workloads.cfg2_tiles(torch.from_numpy(luts["3inst"]))
+    assert tiles.shape == (65536, 256) and tiles.dtype == torch.float32
+    mine = tiles[torch.from_numpy(g["index"])].numpy()
+    assert np.allclose(mine, g["tiles"], rtol=0, atol=2e-5)
+    assert abs(float(tiles.square().mean().sqrt()) - float(g["z_rms"])) < 1e-4
+
+
+def test_resume_ignores_stale_or_foreign_files(tmp_path):
+    """The resume check of ``encode_model`` is pure host logic: exercised here with a stand-in for the encoder."""
+    from trellis_b200 import model
+    import json
+    shapes = {"model.layers.0.self_attn.k_proj": (32, 64)}
+    calls = []
+
+    def fake_encode_matrix(w, K, codebook, seed, H=None, return_ip=False, **kw):
+        calls.append((K, seed))
+        n, k = w.shape
+        packed = torch.full(((n // 16) * (k // 16), 8 * K), len(calls), dtype=torch.int32)
+        return packed, w, 0.0, None
+
+    real = model.encode_matrix, model.qtip.workspace_status, model.qtip.codebook_id
+    model.encode_matrix = fake_encode_matrix
+    model.qtip.workspace_status = lambda *a, **k: None
+
+    class _S:
+        def synchronize(self):
+            pass
+
+    try:
+        import unittest.mock as um
+        with um.patch.object(torch.cuda, "current_stream", lambda dev=None: _S()), \
+                um.patch.object(torch.cuda, "current_device", lambda: 0):
+            run = lambda **kw: model.encode_model(shapes, hessian_fn=None, weight_fn=lambda n, s, d: torch.zeros(s), out_dir=str(tmp_path),
+                                                  device=torch.device("cpu"), gather=False, **kw)
+            r1, _ = run(K=3, codebook="mcg")
+            assert not r1["model.layers.0.self_attn.k_proj"]["skipped"] and len(calls) == 1
+            r2, _ = run(K=3, codebook="mcg")
+            assert r2["model.layers.0.self_attn.k_proj"]["skipped"] and len(calls) == 1          # same settings: resumed
+            r3, _ = run(K=4, codebook="mcg")
+            assert not r3["model.layers.0.self_attn.k_proj"]["skipped"] and len(calls) == 2      # other K: encoded again
+            r4, _ = run(K=4, codebook="3inst")
+            assert not r4["model.layers.0.self_attn.k_proj"]["skipped"] and len(calls) == 3      # other codebook
+            r5, _ = run(K=4, codebook="3inst", seed_fn=lambda n: 7)
+            assert not r5["model.layers.0.self_attn.k_proj"]["skipped"] and len(calls) == 4      # other seed
+            meta = json.load(open(os.path.join(tmp_path, "model.layers.0.self_attn.k_proj.bits.npy.json")))
+            assert meta == {"K": 4, "codebook": "3inst", "shape": [32, 64], "seed": 7, "ldlq": False}
+            os.remove(os.path.join(tmp_path, "model.layers.0.self_attn.k_proj.bits.npy.json"))
+            r6, _ = run(K=4, codebook="3inst", seed_fn=lambda n: 7)
+            assert not r6["model.layers.0.self_attn.k_proj"]["skipped"]                          # no side-car: not trusted
+    finally:
+        model.encode_matrix, model.qtip.workspace_status, model.qtip.codebook_id = real

@@ -106,3 +106,36 @@ def test_encoding_a_reconstruction_is_lossless(oracle, golden, luts):
     dq = golden["encode"]["3inst_K3_dq"]
     _, dq2, sse = oracle.viterbi_tb(dq, 3, luts["3inst"], with_sse=True)
     assert same_bits(dq, dq2) and float(sse.max()) == 0.0
+
+
+# First 16 hex digits of sha256(symbols as uint8, row-major) that the reference's ``viterbi_tb(w, K, lut)`` (fp32 DP,
+# torch CPU) gives on ``torch.manual_seed(0); w = torch.randn(256, 256)[:64]``, written down from a run of the
+# reference that was independent of the one that made tests/golden/encode.npz.
+REFERENCE_SYMBOL_DIGESTS = {
+    ("1mad", 2): "eeb3b7fceca53b36", ("1mad", 3): "c53c13668c3c4bd2", ("1mad", 4): "a208c9b2c9f09a1b",
+    ("3inst", 2): "f06b0c366c4357ba", ("3inst", 3): "116385363d10203d", ("3inst", 4): "160b4edf586c89af",
+    ("mcg", 2): "e2986c2f4e9e1b5d", ("mcg", 3): "385e33af294e2021", ("mcg", 4): "0d559459225b0b63",
+}
+
+
+@pytest.mark.parametrize("K", KS)
+@pytest.mark.parametrize("name", CODEBOOKS)
+def test_viterbi_tb_matches_reference_on_64_tiles(oracle, golden, luts, name, K):
+    g = golden["encode"]
+    w = g["w64"]
+    assert w.shape == (64, 256) and np.array_equal(w[:6], g["w"])
+    bits, dq = oracle.viterbi_tb(w, K, luts[name])
+    key = f"{name}_K{K}"
+    assert np.array_equal(bits, g[key + "_bits64"].astype(np.int64))
+    sha = np.frombuffer(hashlib.sha256(np.ascontiguousarray(dq).tobytes()).digest(), dtype=np.uint8)
+    assert np.array_equal(sha, g[key + "_dq64_sha256"])
+    assert hashlib.sha256(bits.astype(np.uint8).tobytes()).hexdigest()[:16] == REFERENCE_SYMBOL_DIGESTS[(name, K)]
+
+
+def test_viterbi_tb_on_tiles_of_the_second_configuration(oracle, golden, luts):
+    """16 tiles spread over the 4096 x 4096 outlier matrix, exactly as the reference's IPContext made them."""
+    g = golden["cfg2_probe"]
+    assert g["tiles"].shape == (16, 256) and int(g["index"][-1]) == 65535
+    bits, dq = oracle.viterbi_tb(g["tiles"], 3, luts["3inst"])
+    assert np.array_equal(bits, g["bits"].astype(np.int64))
+    assert same_bits(dq, g["dq"])

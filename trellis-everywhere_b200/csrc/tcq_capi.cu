@@ -106,11 +106,80 @@ int check_common(int K, int codebook, long long n) {
 
 bool misaligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a != 0; }
 
+// What one tail-biting encode reads and writes; tiles (ld == 0) or an LDLQ row block (ld > 0).
+struct EncodeIO {
+    const float* w;
+    const float* w_add;
+    long long ld;
+    long long n;               // tiles
+    uint32_t* packed;
+    long long packed_stride;
+    int64_t* bits;
+    float* dq;
+    float* sse;
+    float* wq;
+    float* err;
+};
+
+// The launch sequence of the tail-biting encoder (src/trellis/qtip.py:135-144) per workspace chunk:
+// step kernel on the rotated tile -> traceback to the overlap -> step kernel tied to the overlap -> traceback.
+// The first step kernel of the call clears the workspace's status word itself (no separate memset node).
+int encode_core(const EncodeIO& io, int K, int codebook, void* ws, size_t ws_bytes, cudaStream_t s) {
+    int rc, num_sms = 0;
+    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
+    Workspace wk;
+    if ((rc = carve(ws, ws_bytes, io.n, K, num_sms, &wk)) != TCQ_OK) return rc;
+    // start of chunk c0 inside w / w_add / wq / err: whole tiles (1 KiB each) or 16 columns of the row block per tile
+    const long long tile_step = io.ld > 0 ? 16 : kT;
+    for (long long c0 = 0; c0 < io.n; c0 += wk.chunk) {
+        const long long cn = io.n - c0 < wk.chunk ? io.n - c0 : wk.chunk;
+        const float* w = io.w + c0 * tile_step;
+        const float* w_add = io.w_add ? io.w_add + c0 * tile_step : nullptr;
+        cudaError_t err;
+        // pass 1: tile rotated by half its length, free start; only the second half of the
+        // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
+        ForwardArgs f1{w, w_add, io.ld, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f, 0, wk.status,
+                       c0 == 0 ? kFwdResetStatus : 0};
+        int nkeys = 0;
+        if ((err = forward(K, codebook, f1, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
+        TracebackArgs t1{};
+        t1.bp = wk.bp;
+        t1.n = cn;
+        t1.bp_steps = kT / 2;
+        t1.codebook = codebook;
+        t1.e_start = wk.e_final;
+        t1.keys = nkeys ? wk.keys : nullptr;
+        t1.nkeys = nkeys;
+        t1.e_out = wk.overlap;
+        if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
+        // pass 2: true order, start and end tied to the overlap (qtip.py:142)
+        ForwardArgs f2{w, w_add, io.ld, cn, wk.overlap, 0, kT, wk.bp, nullptr, io.sse ? io.sse + c0 : nullptr, 1.0f, 0,
+                       wk.status, kFwdCheckFinite};
+        if ((err = forward(K, codebook, f2, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
+        TracebackArgs t2{};
+        t2.bp = wk.bp;
+        t2.n = cn;
+        t2.bp_steps = kT;
+        t2.codebook = codebook;
+        t2.e_start = wk.overlap;
+        t2.bits = io.bits ? reinterpret_cast<long long*>(io.bits) + c0 * kT : nullptr;
+        t2.dq = io.dq ? io.dq + c0 * kT : nullptr;
+        t2.packed = io.packed ? io.packed + c0 * io.packed_stride : nullptr;
+        t2.packed_stride = io.packed_stride;
+        t2.wq = io.wq ? io.wq + c0 * tile_step : nullptr;
+        t2.err = io.err ? io.err + c0 * tile_step : nullptr;
+        t2.src = io.w + c0 * tile_step;
+        t2.ld = io.ld;
+        if ((err = launch_traceback(K, t2, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 2");
+    }
+    return TCQ_OK;
+}
+
 }  // namespace
 
 extern "C" {
 
-int tcq_abi_version(void) { return 3; }
+int tcq_abi_version(void) { return 4; }
 
 const char* tcq_strerror(int code) {
     switch (code) {
@@ -161,34 +230,40 @@ int tcq_encode_tb(const float* w, int64_t n_tiles, int K, int codebook, uint32_t
     if (misaligned(w, 16) || misaligned(packed, 4) || (dq && misaligned(dq, 4)) || (bits && misaligned(bits, 8)) ||
         (sse && misaligned(sse, 4)))
         return TCQ_E_MISALIGNED;
-    int num_sms = 0;
-    if ((rc = current_num_sms(&num_sms)) != TCQ_OK) return rc;
-    Workspace wk;
-    if ((rc = carve(ws, ws_bytes, n_tiles, K, num_sms, &wk)) != TCQ_OK) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int nw = kT * K / 32;
-    if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
+    EncodeIO io{};
+    io.w = w;
+    io.n = n_tiles;
+    io.packed = packed;
+    io.packed_stride = kT * K / 32;
+    io.bits = bits;
+    io.dq = dq;
+    io.sse = sse;
+    return encode_core(io, K, codebook, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
 
-    for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
-        const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
-        cudaError_t err;
-        // pass 1: tile rotated by half its length, free start; only the second half of the
-        // backpointers is needed to reach the state at rotated position 128 (qtip.py:138-141)
-        ForwardArgs f1{w + c0 * kT, cn, nullptr, kT / 2, kT / 2, wk.bp, wk.e_final, nullptr, 1.0f, 0, wk.status};
-        int nkeys = 0;
-        if ((err = forward(K, codebook, f1, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 1");
-        TracebackArgs t1{wk.bp, cn, kT / 2, codebook, wk.e_final, nkeys ? wk.keys : nullptr, nkeys, wk.overlap,
-                         nullptr, nullptr, nullptr, nullptr};
-        if ((err = launch_traceback(K, t1, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 1");
-        // pass 2: true order, start and end tied to the overlap (qtip.py:142)
-        ForwardArgs f2{w + c0 * kT, cn, wk.overlap, 0, kT, wk.bp, nullptr, sse ? sse + c0 : nullptr, 1.0f, 0, wk.status};
-        if ((err = forward(K, codebook, f2, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward pass 2");
-        TracebackArgs t2{wk.bp, cn, kT, codebook, wk.overlap, nullptr, 0, nullptr, nullptr,
-                         bits ? reinterpret_cast<long long*>(bits) + c0 * kT : nullptr, dq ? dq + c0 * kT : nullptr,
-                         packed + c0 * nw};
-        if ((err = launch_traceback(K, t2, s)) != cudaSuccess) return cuda_fail(err, "traceback pass 2");
-    }
-    return TCQ_OK;
+int tcq_encode_tb_rows(const float* src, const float* comp, int64_t ld, int64_t n_out, int K, int codebook,
+                       uint32_t* packed, int64_t packed_stride, float* wq, float* err, float* sse, void* ws,
+                       size_t ws_bytes, void* stream) {
+    int rc = check_common(K, codebook, n_out);
+    if (rc != TCQ_OK) return rc;
+    if (n_out % 16 || ld < n_out) return TCQ_E_BAD_ARGUMENT;
+    if (packed != nullptr && packed_stride < kT * K / 32) return TCQ_E_BAD_ARGUMENT;
+    if (n_out == 0) return TCQ_OK;
+    if (src == nullptr || wq == nullptr) return TCQ_E_NULL_POINTER;
+    if (misaligned(src, 4) || (comp && misaligned(comp, 4)) || misaligned(wq, 4) || (err && misaligned(err, 4)) ||
+        (packed && misaligned(packed, 4)) || (sse && misaligned(sse, 4)))
+        return TCQ_E_MISALIGNED;
+    EncodeIO io{};
+    io.w = src;
+    io.w_add = comp;
+    io.ld = ld;
+    io.n = n_out / 16;
+    io.packed = packed;
+    io.packed_stride = packed_stride;
+    io.sse = sse;
+    io.wq = wq;
+    io.err = err;
+    return encode_core(io, K, codebook, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const int32_t* overlap, int roll,
@@ -209,13 +284,20 @@ int tcq_viterbi_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     for (long long c0 = 0; c0 < n_tiles; c0 += wk.chunk) {
         const long long cn = n_tiles - c0 < wk.chunk ? n_tiles - c0 : wk.chunk;
         cudaError_t err;
-        ForwardArgs f{w + c0 * kT, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
-                      overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0, wk.status};
+        ForwardArgs f{w + c0 * kT, nullptr, 0, cn, overlap ? overlap + c0 : nullptr, roll, kT, wk.bp,
+                      overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0, wk.status, kFwdCheckFinite};
         int nkeys = 0;
         if ((err = forward(K, codebook, f, wk, num_sms, s, &nkeys)) != cudaSuccess) return cuda_fail(err, "forward");
         const bool use_keys = overlap == nullptr && nkeys > 0;
-        TracebackArgs t{wk.bp, cn, kT, codebook, overlap ? overlap + c0 : wk.e_final, use_keys ? wk.keys : nullptr, nkeys, nullptr,
-                        reinterpret_cast<long long*>(states) + c0 * kT, nullptr, nullptr, nullptr};
+        TracebackArgs t{};
+        t.bp = wk.bp;
+        t.n = cn;
+        t.bp_steps = kT;
+        t.codebook = codebook;
+        t.e_start = overlap ? overlap + c0 : wk.e_final;
+        t.keys = use_keys ? wk.keys : nullptr;
+        t.nkeys = nkeys;
+        t.states = reinterpret_cast<long long*>(states) + c0 * kT;
         if ((err = launch_traceback(K, t, s)) != cudaSuccess) return cuda_fail(err, "traceback");
     }
     return TCQ_OK;
@@ -236,7 +318,8 @@ int tcq_forward_pass(const float* w, int64_t n_tiles, int K, int codebook, const
     if (wk.chunk < n_tiles) return TCQ_E_WORKSPACE;
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess)
         return cuda_fail(cudaGetLastError(), "status reset");
-    ForwardArgs f{w, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0, wk.status};
+    ForwardArgs f{w, nullptr, 0, n_tiles, overlap, roll, bp_steps, wk.bp, overlap ? nullptr : wk.e_final, nullptr, 1.0f, 0,
+                  wk.status, kFwdCheckFinite};
     int nkeys = 0;
     cudaError_t err = forward(K, codebook, f, wk, num_sms, static_cast<cudaStream_t>(stream), &nkeys);
     return err == cudaSuccess ? TCQ_OK : cuda_fail(err, "forward");
@@ -272,7 +355,7 @@ int tcq_selftest_wait_timeout(const float* w, int64_t n_tiles, int K, void* ws, 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(wk.status, 0, sizeof(unsigned int), s) != cudaSuccess) return cuda_fail(cudaGetLastError(), "status reset");
     // the buffers of the final metrics are told to expect 16 bytes more than the cluster will ever send
-    ForwardArgs f{w, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16, wk.status};
+    ForwardArgs f{w, nullptr, 0, n_tiles, nullptr, 0, kT, wk.bp, wk.e_final, nullptr, 1.0f, 16, wk.status, 0};
     int nkeys = 0;
     cudaError_t err = forward(K, kCbMcg, f, wk, num_sms, s, &nkeys);
     if (err != cudaSuccess) return cuda_fail(err, "forward (self-test)");

@@ -38,8 +38,15 @@
 
 namespace tcq {
 
+// ForwardArgs::flags
+constexpr int kFwdResetStatus = 1;   // clear the status word at kernel start (the first launch of a call only)
+constexpr int kFwdCheckFinite = 2;   // flag NaN / infinite weights in the status word
+
 struct ForwardArgs {
-    const float* w;          // [n,256] tiles
+    const float* w;          // [n,256] tiles, or (ld > 0) a 16-row block of a row-major matrix
+    const float* w_add;      // nullptr, or a second operand of the same layout: the kernel encodes fl(w + w_add)
+    long long ld;            // 0: tiles.  > 0: weight t of tile i is w[(t & 15) * ld + 16 * i + (t >> 4)], the LDLQ
+                             //    row-block layout of src/trellis/ldlq.py:138-140 (16 input channels x n_out)
     long long n;             // tiles in this launch
     const int* overlap;      // [n] forced first/last edge, or nullptr (unconstrained, metrics start at 0)
     int roll;                // step t consumes w[(t + roll) & 255]   (roll = 128: torch.roll(w,128))
@@ -50,7 +57,23 @@ struct ForwardArgs {
     float one;               // must be 1.0f: run-time constant of the fused arithmetic tricks (see tcq_common.cuh)
     int inject_extra_bytes;  // 0; the wait self-test sets 16 so that the cluster kernel's byte counts can never be met
     unsigned int* status;    // device word or nullptr: bit 0 = a bounded wait gave up, bit 1 = a weight was NaN or infinite
+    int flags;               // kFwdResetStatus | kFwdCheckFinite
 };
+
+// Weight j of the staging order for tile `tile`: returns the value and the step index t it belongs to.
+// Tiles: t = j.  Row block: consecutive j walk along a matrix row (coalesced), t = (j & 15) * 16 + (j >> 4).
+__device__ __forceinline__ float load_weight(const ForwardArgs& a, long long tile, int j, int& t) {
+    long long off;
+    if (a.ld == 0) {
+        t = j;
+        off = tile * kT + j;
+    } else {
+        t = ((j & 15) << 4) | (j >> 4);
+        off = (long long)(j >> 4) * a.ld + tile * 16 + (j & 15);
+    }
+    const float x = a.w[off];
+    return a.w_add != nullptr ? __fadd_rn(x, a.w_add[off]) : x;
+}
 
 template <int K, int G>
 constexpr size_t forward_smem_bytes() {
@@ -82,6 +105,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
     const float kInf = __uint_as_float(kInfBits);
     const f32x2 one2 = pack2(a.one, a.one);
     const float zero = a.one - 1.0f;
+    if ((a.flags & kFwdResetStatus) && blockIdx.x == 0 && tid == 0 && a.status != nullptr) atomicExch(a.status, 0u);
 
     for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
         const long long tile0 = grp * G;
@@ -89,9 +113,10 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_kernel(const ForwardArgs a)
         // ---- load the group's weights, initialise the metrics (qtip.py:161-165) ----
         for (int i = tid; i < G * kT; i += NT) {
             const long long tile = tile0 + (i >> 8);
-            const float x = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
-            wv[i] = x;
-            if (!isfinite(x) && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
+            int t = i & 255;
+            const float x = tile < a.n ? load_weight(a, tile, i & 255, t) : 0.0f;
+            wv[(i & ~255) | t] = x;
+            if ((a.flags & kFwdCheckFinite) && !isfinite(x) && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
         }
         {
             const float init = constrained ? kInf : 0.0f;

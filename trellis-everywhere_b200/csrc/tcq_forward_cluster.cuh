@@ -85,7 +85,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
     const long long t0 = clock64();
     while (clock64() - t0 < kMbarWaitCycles)
         if (mbar_try_wait(mbar, parity)) return true;
-    return false;
+    // One more poll after the deadline: a thread that was descheduled across it (time slicing, an attached
+    // profiler) must not report a phase that completed meanwhile as lost.
+    return mbar_try_wait(mbar, parity);
 }
 __device__ __forceinline__ void st_async_v4(uint32_t dst, float x, float y, float z, float w, uint32_t mbar) {
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
@@ -210,7 +212,11 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // inflates exactly that one, so that its timeouts happen after the last store has landed.)
     auto wait_buffer = [&](int s, int b, bool last) {
         const uint32_t m = smem_u32(mbar + (2 * s + b));
-        if (!mbar_wait(m, (parity >> (2 * s + b)) & 1u)) timed_out = true;
+        // Fast path first; a thread that has already given up once polls once and never spins again, so a
+        // launch whose protocol broke still finishes in about one time limit, not one per wait.
+        if (!mbar_try_wait(m, (parity >> (2 * s + b)) & 1u)) {
+            if (timed_out || !mbar_wait(m, (parity >> (2 * s + b)) & 1u)) timed_out = true;
+        }
         parity ^= 1u << (2 * s + b);
         if (tid == 0 && !timed_out) mbar_expect(m, kBufBytes + (last ? uint32_t(a.inject_extra_bytes) : 0u));
     };
@@ -293,6 +299,8 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         wait_pending = true;          // the phase entered above is closed during the next step_set
     };
 
+    if ((a.flags & kFwdResetStatus) && blockIdx.x == 0 && tid == 0 && a.status != nullptr) atomicExch(a.status, 0u);
+
     // ---- mbarriers: one arrival (the re-arming thread) plus kBufBytes of stores per phase ----
     if (tid == 0) {
 #pragma unroll
@@ -310,9 +318,10 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
         // ---- weights and initial metrics (src/trellis/qtip.py:161-165) ----
         for (int i = tid; i < G * kT; i += NT) {
             const long long tile = tile0 + (i >> 8);
-            const float x = tile < a.n ? a.w[tile * kT + (i & 255)] : 0.0f;
-            wv[i] = x;
-            if (!isfinite(x) && rank == 0 && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
+            int t = i & 255;
+            const float x = tile < a.n ? load_weight(a, tile, i & 255, t) : 0.0f;
+            wv[(i & ~255) | t] = x;
+            if ((a.flags & kFwdCheckFinite) && !isfinite(x) && rank == 0 && a.status != nullptr) atomicOr(a.status, 2u);   // reported, never trapped on
         }
         {
             const float init = constrained ? kInf : 0.0f;

@@ -10,12 +10,36 @@
 
 namespace tcq {
 
+constexpr int kMaxDeviceOrdinals = 64;
+
+// Current device ordinal, or -1 if it does not fit the per-device caches below (then nothing is cached).
+static inline cudaError_t device_slot(int* slot) {
+    int dev = 0;
+    const cudaError_t err = cudaGetDevice(&dev);
+    *slot = (err == cudaSuccess && dev >= 0 && dev < kMaxDeviceOrdinals) ? dev : -1;
+    return err;
+}
+
+// Per kernel instantiation and device, once: opt in to the kernel's dynamic shared memory.  Small
+// encoder calls (an LDLQ block is a few hundred tiles) would otherwise pay for the attribute call
+// on every launch.  (Racing first calls from two host threads both set the same value.)
+template <typename Kern>
+static cudaError_t ensure_smem_optin(Kern kern, size_t smem, bool (&done)[kMaxDeviceOrdinals], int slot) {
+    if (slot >= 0 && done[slot]) return cudaSuccess;
+    const cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (err == cudaSuccess && slot >= 0) done[slot] = true;
+    return err;
+}
+
 template <int K, int CB, int G, int NT, int LU>
 static cudaError_t launch_variant(const ForwardArgs& a, int num_sms, cudaStream_t stream) {
     auto kern = tcq_forward_kernel<K, CB, G, NT, LU>;
     constexpr size_t smem = forward_smem_bytes<K, G>();
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    static bool optin[kMaxDeviceOrdinals] = {false};
+    int slot = -1;
+    cudaError_t err = device_slot(&slot);
     if (err != cudaSuccess) return err;
+    if ((err = ensure_smem_optin(kern, smem, optin, slot)) != cudaSuccess) return err;
     const long long ngroups = (a.n + G - 1) / G;
     const int grid = int(ngroups < num_sms ? ngroups : num_sms);
     kern<<<grid, NT, smem, stream>>>(a);
@@ -28,8 +52,11 @@ template <int K, int CB, int C, int GS, int NT, int LU>
 static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long long* keys, cudaStream_t stream) {
     auto kern = tcq_forward_cluster_kernel<K, CB, C, GS, NT, LU>;
     constexpr size_t smem = cluster_smem_bytes<K, C, GS>();
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    static bool optin[kMaxDeviceOrdinals] = {false};
+    int dev = -1;
+    cudaError_t err = device_slot(&dev);
     if (err != cudaSuccess) return err;
+    if ((err = ensure_smem_optin(kern, smem, optin, dev)) != cudaSuccess) return err;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = C;
@@ -42,16 +69,17 @@ static cudaError_t launch_cluster_variant(const ForwardArgs& a, unsigned long lo
     cfg.stream = stream;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    static int max_clusters[64] = {0};            // per device ordinal; 0 = not queried yet, -1 = unsupported
-    int dev = 0;
-    if ((err = cudaGetDevice(&dev)) != cudaSuccess) return err;
-    int maxc = dev >= 0 && dev < 64 ? max_clusters[dev] : 0;
+    static int max_clusters[kMaxDeviceOrdinals] = {0};   // per device ordinal; 0 = not known yet, -1 = cannot schedule this cluster
+    int maxc = dev >= 0 ? max_clusters[dev] : 0;
     if (maxc == 0) {
         int q = 0;
         err = cudaOccupancyMaxActiveClusters(&q, kern, &cfg);
-        if (err != cudaSuccess) { (void)cudaGetLastError(); q = 0; }
+        if (err != cudaSuccess) {
+            (void)cudaGetLastError();              // a failed query says nothing about the device: ask again next time
+            return cudaErrorNotSupported;
+        }
         maxc = q > 0 ? q : -1;
-        if (dev >= 0 && dev < 64) max_clusters[dev] = maxc;
+        if (dev >= 0) max_clusters[dev] = maxc;    // cached only when the query itself succeeded
     }
     if (maxc < 0) return cudaErrorNotSupported;
     constexpr int G = 2 * GS;

@@ -17,6 +17,10 @@
 //     row, argmin edge and overlap word is produced before it is consumed), so nothing has to be
 //     cleared; but two calls whose kernels overlap on the GPU (different streams, no dependency)
 //     overwrite each other's backpointers.  Serialise them.
+//   * tcq_encode_tb_static_status(stream) is tcq_workspace_status for this path: the status word
+//     (a bounded in-kernel wait gave up / a weight was NaN or infinite) lives inside the array, where a
+//     caller without the array's address could not otherwise read it.  It reports on the LAST call made
+//     on the current device and synchronises the stream.
 //
 // The name of a __device__ array is, in host code, only a handle for the runtime: it is not a
 // device address, and handing it to a kernel would make the kernel fault or scribble over
@@ -30,10 +34,14 @@ namespace {
 static __device__ __align__(256) unsigned char g_static_scratch[TCQ_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {nullptr};
+void* g_scratch_addr[kMaxDevices] = {nullptr};     // written once per device with the same value by whoever comes first
+
+// Batch size and K of the last call on each device: the status word's place inside the array depends on them.
+struct LastCall { long long n; int K; };
+LastCall g_last_call[kMaxDevices] = {};
 
 // Device address of the scratch array on the current device (looked up once per device).
-int scratch_for_current_device(void** out) {
+int scratch_for_current_device(void** out, int* dev_out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -50,6 +58,7 @@ int scratch_for_current_device(void** out) {
         g_scratch_addr[dev] = p;
     }
     *out = g_scratch_addr[dev];
+    if (dev_out != nullptr) *dev_out = dev;
     return TCQ_OK;
 }
 
@@ -59,9 +68,15 @@ extern "C" {
 
 int64_t tcq_encode_tb_static_max_tiles(int K) {
     if (K < 2 || K > 4) return TCQ_E_BAD_K;
-    int64_t n = 0;
-    while (tcq_workspace_bytes(n + 1, K) <= size_t(TCQ_STATIC_SCRATCH_BYTES)) ++n;
-    return n;
+    // Worked out once per K.  Batches this small are far below one full-speed chunk, where the workspace
+    // size depends on the tile count and K only, not on the device.
+    static int64_t cached[5] = {0, 0, 0, 0, 0};
+    if (cached[K] == 0) {
+        int64_t n = 0;
+        while (tcq_workspace_bytes(n + 1, K) <= size_t(TCQ_STATIC_SCRATCH_BYTES)) ++n;
+        cached[K] = n;
+    }
+    return cached[K];
 }
 
 int tcq_encode_tb_static(const float* w, int64_t n_tiles, int K, int codebook, uint32_t* packed, int64_t* bits,
@@ -71,10 +86,22 @@ int tcq_encode_tb_static(const float* w, int64_t n_tiles, int K, int codebook, u
     if (n_tiles > tcq_encode_tb_static_max_tiles(K)) return TCQ_E_TOO_MANY_TILES;
     if (n_tiles == 0) return TCQ_OK;
     void* scratch = nullptr;
-    const int rc = scratch_for_current_device(&scratch);
+    int dev = 0;
+    const int rc = scratch_for_current_device(&scratch, &dev);
     if (rc != TCQ_OK) return rc;
+    g_last_call[dev] = LastCall{n_tiles, K};
     // From here on this is the ordinary encoder with the static array as its workspace.
     return tcq_encode_tb(w, n_tiles, K, codebook, packed, bits, dq, sse, scratch, size_t(TCQ_STATIC_SCRATCH_BYTES), stream);
+}
+
+int tcq_encode_tb_static_status(void* stream) {
+    void* scratch = nullptr;
+    int dev = 0;
+    const int rc = scratch_for_current_device(&scratch, &dev);
+    if (rc != TCQ_OK) return rc;
+    const LastCall last = g_last_call[dev];
+    if (last.n <= 0) return TCQ_OK;                 // nothing has run on this device yet
+    return tcq_workspace_status(scratch, size_t(TCQ_STATIC_SCRATCH_BYTES), last.n, last.K, stream);
 }
 
 }  // extern "C"

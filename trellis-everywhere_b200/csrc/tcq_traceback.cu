@@ -10,9 +10,10 @@
 //   q_t = bp[t][e_t],  s_t = (q_t << (16-K)) | e_t,  e_{t-1} = s_t >> K .
 // Whatever q_t turns out to be, e_{t-1} is one of only Q edges that share the low
 // bits e_t >> K, so lane j < Q fetches row t-1's entry for candidate q = j while
-// the row-t load is still in flight, and the pick is a shuffle.  That halves the
-// length of the dependent chain (two steps per memory round trip).  Afterwards
-// the 32 lanes turn the 256 states held in shared memory into coalesced outputs.
+// the row-t load is still in flight, and the pick is a shuffle; one row further
+// back there are Q*Q possible edges, fetched the same way.  The dependent chain is
+// thus one memory round trip per three steps (two at K = 4).  Afterwards the 32
+// lanes turn the 256 states held in shared memory into coalesced outputs.
 #include "tcq_traceback.cuh"
 
 namespace tcq {
@@ -62,27 +63,50 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const 
     }
     const int t_off = kT - a.bp_steps;             // row r holds step t = r + t_off
 
-    // ---- the walk: two rows per iteration ----
+    // ---- the walk: DEPTH rows per memory round trip ----
+    // Row r's entry is one broadcast load.  Row r-1's entry can only sit at one of Q edges ((j1 << HB) | (e >> K)),
+    // row r-2's at one of Q*Q ((j2 << HB) | (j1 << (HB-K)) | (e >> 2K)); lanes fetch all of them at once and the
+    // picks are shuffles.  (Q*Q = 256 candidates at K = 4 would be 8 loads per lane: two rows per trip there.)
+    constexpr int DEPTH = (K == 4) ? 2 : 3;
+    constexpr int PER = 32 / int(Q) > 0 ? 32 / int(Q) : 1;      // level-2 candidates j2 covered by one load per lane
+    constexpr int NL2 = (int(Q) + PER - 1) / PER;              // level-2 loads per lane
     int r = a.bp_steps - 1;
-    for (; r >= 1; r -= 2) {
-        const uint32_t q_hi = lane == 0 ? bp_entry<K>(bp + size_t(r) * ROWB, e) : 0u;
-        const uint32_t cand_e = ((uint32_t(lane) & (Q - 1)) << HB) | (e >> K);
-        const uint32_t q_lo_c = bp_entry<K>(bp + size_t(r - 1) * ROWB, cand_e);   // lanes >= Q repeat lanes < Q
-        const uint32_t q1 = __shfl_sync(0xffffffffu, q_hi, 0);
+    for (; r >= DEPTH - 1; r -= DEPTH) {
+        const uint32_t q1 = bp_entry<K>(bp + size_t(r) * ROWB, e);
+        const uint32_t j1 = uint32_t(lane) & (Q - 1);
+        const uint32_t e1c = (j1 << HB) | (e >> K);
+        const uint32_t c1 = bp_entry<K>(bp + size_t(r - 1) * ROWB, e1c);          // lanes >= Q repeat lanes < Q
+        uint32_t c2[NL2];
+        if constexpr (DEPTH == 3) {
+#pragma unroll
+            for (int i = 0; i < NL2; ++i) {
+                const uint32_t j2 = (uint32_t(lane) / Q + uint32_t(i * PER)) & (Q - 1);
+                c2[i] = bp_entry<K>(bp + size_t(r - 2) * ROWB, (j2 << HB) | (e1c >> K));
+            }
+        }
         const uint32_t s1 = (q1 << SH) | e;
         const uint32_t e1 = s1 >> K;                                              // == candidate edge of lane q1
-        const uint32_t q0 = __shfl_sync(0xffffffffu, q_lo_c, int(q1));
+        const uint32_t q0 = __shfl_sync(0xffffffffu, c1, int(q1));
         const uint32_t s0 = (q0 << SH) | e1;
+        e = s0 >> K;
         if (lane == 0) {
             st[r + t_off] = uint16_t(s1);
             st[r - 1 + t_off] = uint16_t(s0);
         }
-        e = s0 >> K;
+        if constexpr (DEPTH == 3) {
+            uint32_t pick = c2[0];                                                // q0 is the same in every lane
+#pragma unroll
+            for (int i = 1; i < NL2; ++i) pick = (q0 / PER == uint32_t(i)) ? c2[i] : pick;
+            const uint32_t qm = __shfl_sync(0xffffffffu, pick, int(q1 + Q * (q0 % PER)));
+            const uint32_t sm = (qm << SH) | e;
+            if (lane == 0) st[r - 2 + t_off] = uint16_t(sm);
+            e = sm >> K;
+        }
     }
-    if (r == 0) {                                  // odd row count (not used by the encoder, kept for safety)
-        const uint32_t q = __shfl_sync(0xffffffffu, lane == 0 ? bp_entry<K>(bp, e) : 0u, 0);
+    for (; r >= 0; --r) {                          // the rows left over: one round trip each
+        const uint32_t q = bp_entry<K>(bp + size_t(r) * ROWB, e);
         const uint32_t s = (q << SH) | e;
-        if (lane == 0) st[t_off] = uint16_t(s);
+        if (lane == 0) st[r + t_off] = uint16_t(s);
         e = s >> K;
     }
     if (lane == 0 && a.e_out != nullptr) a.e_out[tile] = int(e);
@@ -95,6 +119,19 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const 
         for (int t = t_off + lane; t < kT; t += 32) a.bits[tile * kT + t] = (long long)(st[t] & (Q - 1));
     if (a.dq != nullptr)
         for (int t = t_off + lane; t < kT; t += 32) a.dq[tile * kT + t] = cb_value_rt(a.codebook, st[t]);
+    if (a.wq != nullptr && t_off == 0) {
+        // LDLQ row-block layout (src/trellis/ldlq.py:142-143): weight t of this tile is element
+        // [t & 15][16 * tile + (t >> 4)] of a 16-row block; j walks along the matrix rows so that a
+        // half-warp writes 64 contiguous bytes.  err = src - reconstruction is the block error the
+        // recursion feeds back (ldlq.py:90,97), formed here instead of by a separate pass over the block.
+        for (int j = lane; j < kT; j += 32) {
+            const int t = ((j & 15) << 4) | (j >> 4);
+            const float v = cb_value_rt(a.codebook, st[t]);
+            const long long off = (long long)(j >> 4) * a.ld + tile * 16 + (j & 15);
+            a.wq[off] = v;
+            if (a.err != nullptr) a.err[off] = __fsub_rn(a.src[off], v);
+        }
+    }
     if (a.packed != nullptr && t_off == 0) {
         // word j holds stream bits 32j .. 32j+31; stream bit p is bit (p % K) of symbol 255 - p / K
         for (uint32_t j = lane; j < NW; j += 32) {
@@ -105,7 +142,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const 
                 const uint32_t t = (kT - 1) - p / K;
                 word |= ((uint32_t(st[t]) >> (p % K)) & 1u) << b;
             }
-            a.packed[tile * NW + j] = word;
+            a.packed[tile * a.packed_stride + j] = word;
         }
     }
 }

@@ -17,7 +17,13 @@ struct TracebackArgs {
     long long* states;         // [n,256] out (only the walked steps are written), or nullptr
     long long* bits;           // [n,256] out: state & (2^K - 1), or nullptr
     float* dq;                 // [n,256] out: codebook value of each state, or nullptr
-    uint32_t* packed;          // [n,8K] out: exporter word layout (needs bp_steps = 256), or nullptr
+    uint32_t* packed;          // [n][packed_stride] out: exporter word layout, 8K words per tile (needs bp_steps = 256), or nullptr
+    long long packed_stride;   // words from one tile's packed codes to the next tile's (>= 8K)
+    // LDLQ row-block outputs (need bp_steps = 256); all three share the layout [16][ld], tile i = columns 16i..16i+15
+    float* wq;                 // out: reconstruction, or nullptr
+    float* err;                // out: src - reconstruction, or nullptr
+    const float* src;          // in: the uncompensated block (read only when err != nullptr)
+    long long ld;
 };
 
 cudaError_t launch_traceback(int K, const TracebackArgs& args, cudaStream_t stream);

@@ -13,7 +13,7 @@ import subprocess
 _CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 LIB_PATH = os.path.join(_CSRC, "libtcq_b200.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # name -> (restype, argtypes); mirrors include/tcq_b200.h one to one
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -26,6 +26,8 @@ SIGNATURES = {
     "tcq_encode_tb": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "tcq_encode_tb_static_max_tiles": (_i64, [_int]),
     "tcq_encode_tb_static": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]),
+    "tcq_encode_tb_static_status": (_int, [_vp]),
+    "tcq_encode_tb_rows": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "tcq_viterbi_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
     "tcq_forward_pass": (_int, [_vp, _i64, _int, _int, _vp, _int, _int, _vp, _sz, _vp]),
     "tcq_workspace_status": (_int, [_vp, _sz, _i64, _int, _vp]),

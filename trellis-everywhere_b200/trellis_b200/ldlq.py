@@ -13,8 +13,9 @@ from typing import Callable, Optional
 
 import torch
 
+from . import qtip as _qtip
 from .qtip import (T_SEQ, CodebookLike, IPContext, _check_backend, _cuda_device, _pow2_block, block_hadamard,
-                   codebook_id, codebook_lut, encode, CODEBOOK_NAMES)
+                   codebook_id, codebook_lut, encode, encode_rows, CODEBOOK_NAMES)
 
 
 def regularize_H(H: torch.Tensor, sigma_reg: float = 0.025) -> torch.Tensor:
@@ -65,7 +66,12 @@ def ldlq(Wt: torch.Tensor, L: torch.Tensor, enc: Callable[[torch.Tensor], torch.
     the factor from ``block_ldl``; ``enc`` quantises one compensated ``(16, n)`` row
     block.  Rows are visited from the last 16-row block to the first; inside a span
     of ``buf`` rows the correction uses the span's own errors, and after a span is
-    finished its errors are pushed to all earlier rows with one fp32 GEMM.
+    finished its errors are pushed to all earlier rows with one fp32 GEMM.  (The
+    reference pushes them to every row, ldlq.py:97-98; rows of finished spans are never
+    read again and L is zero above its diagonal, so only the earlier rows are updated here.)
+
+    This is the general form for any ``enc``; ``ldlq_b200`` is the same recursion with the
+    encoder step fused into the B200 kernels.
     """
     k, n = Wt.shape
     src = Wt.float()
@@ -80,28 +86,76 @@ def ldlq(Wt: torch.Tensor, L: torch.Tensor, enc: Callable[[torch.Tensor], torch.
             if bj < hi:                                                   # errors of the span's later blocks
                 carry[bi:bj].addmm_(Lf[bj:hi, bi:bj].t(), src[bj:hi] - Wq[bj:hi])
             Wq[bi:bj] = enc(src[bi:bj] + carry[bi:bj]).float()
-        carry.addmm_(Lf[lo:hi].t(), src[lo:hi] - Wq[lo:hi])
+        if lo > 0:
+            carry[:lo].addmm_(Lf[lo:hi, :lo].t(), src[lo:hi] - Wq[lo:hi])
         hi = lo
     return Wq.to(Wt.dtype)
 
 
 @torch.no_grad()
-def ldlq_row_groups(Wt: torch.Tensor, L: torch.Tensor, make_enc_for: Callable[[int, int], Callable], groups: int = 2,
-                    buf: int = 128) -> torch.Tensor:
+def ldlq_b200(Wt: torch.Tensor, L: torch.Tensor, K: int, codebook: CodebookLike, buf: int = 128,
+              packed: Optional[torch.Tensor] = None, tap: Optional[Callable] = None) -> torch.Tensor:
+    """``ldlq`` (ldlq.py:72-99) with the encoder step running in place on the recursion's matrices.
+
+    Per 16-row block the general form costs a subtraction, a GEMM, an addition, a transposing copy, the
+    encoder, another transposing copy, a copy into ``Wq`` and (for an exporter) a copy of the packed words;
+    here it is the GEMM plus one ``encode_rows`` call: the step kernel reads ``src + carry`` straight from the
+    row block, and the traceback kernel writes the reconstruction, the block error ``src - Wq`` and the packed
+    words to their final places.  Same arithmetic in the same order, so the codes equal those of
+    ``ldlq(Wt, L, make_enc(K, codebook))`` bit for bit.
+
+    ``packed``: optional int32 ``[n/16, k/16, 8K]`` array that receives every tile's code words in the
+    exporter's tile order (export_packed_8b.py:114-131).  ``tap(bi, src_block, carry_block, wq_block)`` (optional)
+    is called after each block's encoder call has been queued, with views of that block's 16 rows (for tests that
+    record what the encoder was given and what it returned).  Returns ``Wq (k, n)``.
+    """
+    k, n = Wt.shape
+    if k % 16 or n % 16:
+        raise ValueError(f"shape {(k, n)} not 16-divisible")
+    src = Wt.float().contiguous()
+    Lf = L.float()
+    Wq = torch.empty_like(src)
+    err = torch.empty_like(src)            # src - Wq of the finished blocks, written by the encoder
+    carry = torch.zeros_like(src)
+    cid = codebook_id(codebook)
+    hi = k
+    while hi > 0:
+        lo = max(hi - buf, 0)
+        for bj in range(hi, lo, -16):
+            bi = bj - 16
+            if bj < hi:
+                carry[bi:bj].addmm_(Lf[bj:hi, bi:bj].t(), err[bj:hi])
+            encode_rows(src[bi:bj], carry[bi:bj], K, cid, Wq[bi:bj], err[bi:bj],
+                        packed[:, bi // 16] if packed is not None else None)
+            if tap is not None:
+                tap(bi, src[bi:bj], carry[bi:bj], Wq[bi:bj])
+        if lo > 0:
+            carry[:lo].addmm_(Lf[lo:hi, :lo].t(), err[lo:hi])
+        hi = lo
+    return Wq.to(Wt.dtype)
+
+
+@torch.no_grad()
+def ldlq_row_groups(Wt: torch.Tensor, L: torch.Tensor, make_enc_for: Optional[Callable[[int, int], Callable]], groups: int = 2,
+                    buf: int = 128, fused: Optional[Callable[[torch.Tensor, int, int], torch.Tensor]] = None) -> torch.Tensor:
     """``ldlq`` with the output channels (columns of ``Wt``) cut into ``groups`` slices that run side by side.
 
     The recursion couples input channels only, so column slices of ``Wt`` are independent problems with the same
     ``L``.  One recursion issues encoder calls of ``n/16`` tiles one after another, which rarely fill the last round
     of SMs (256 tiles occupy 64 of a B200's 74 SM pairs); slices on separate CUDA streams (one host thread each) let
     one slice's kernels take the SMs the other leaves idle.  ``make_enc_for(a, b)`` returns the ``enc`` closure for
-    columns ``a:b`` (16-aligned).  Equal to ``ldlq`` up to the summation order of the feedback GEMMs, whose
-    column count differs.
+    columns ``a:b`` (16-aligned); alternatively ``fused(Wt_slice, a, b)`` runs a slice's whole recursion (the
+    ``ldlq_b200`` form).  Equal to ``ldlq`` up to the summation order of the feedback GEMMs, whose column count differs.
     """
     import threading
     k, n = Wt.shape
     groups = max(1, min(int(groups), n // 16))
+
+    def solve(part: torch.Tensor, a: int, b: int) -> torch.Tensor:
+        return fused(part, a, b) if fused is not None else ldlq(part, L, make_enc_for(a, b), buf)
+
     if groups == 1:
-        return ldlq(Wt, L, make_enc_for(0, n), buf)
+        return solve(Wt, 0, n)
     per = -(-(n // 16) // groups) * 16
     bounds = [(a, min(a + per, n)) for a in range(0, n, per)]
     out = torch.empty_like(Wt)
@@ -114,9 +168,12 @@ def ldlq_row_groups(Wt: torch.Tensor, L: torch.Tensor, make_enc_for: Callable[[i
             with torch.cuda.device(dev):
                 s = torch.cuda.Stream(dev)
                 s.wait_stream(caller)
-                with torch.cuda.stream(s):
-                    out[:, a:b] = ldlq(Wt[:, a:b].contiguous(), L, make_enc_for(a, b), buf)
-                s.synchronize()
+                try:
+                    with torch.cuda.stream(s):
+                        out[:, a:b] = solve(Wt[:, a:b].contiguous(), a, b)
+                    s.synchronize()
+                finally:
+                    _qtip.release_workspace(dev, s)     # this stream is never used again
         except BaseException as e:          # surfaced by the caller below
             errors.append(e)
 
@@ -186,5 +243,6 @@ def tcq_quantize_weight_ldlq(w: torch.Tensor, K: int, lut: CodebookLike, H: torc
     Lm = block_ldl(regularize_H(Ht, sigma_reg), b=16)
     if Lm is None:                                  # degenerate Hessian: no feedback for this matrix (ldlq.py:148-151)
         Lm = torch.zeros(k, k, device=dev)
-    zq_t = ldlq_row_groups(ip.z.t().contiguous(), Lm, lambda a, b: make_enc(K, lut), row_groups)
+    zq_t = ldlq_row_groups(ip.z.t().contiguous(), Lm, None, row_groups,
+                           fused=lambda part, a, b: ldlq_b200(part, Lm, K, lut))
     return ip.restore(zq_t.t().contiguous()).to(dtype=w.dtype, device=w.device)

@@ -110,17 +110,10 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
         if Lm is None:
             Lm = torch.zeros(k, k, device=dev)
         store = torch.empty((n // 16, k // 16, nw), dtype=torch.int32, device=dev)
-
-        def enc_for(a: int, b: int):       # output channels a:b; encoder calls arrive from the last 16-column block to the first
-            col = [k // 16]
-
-            def sink(p):
-                col[0] -= 1
-                store[a // 16:b // 16, col[0]] = p
-
-            return tldlq.make_enc(K, codebook, sink)
-
-        zq = tldlq.ldlq_row_groups(ip.z.t().contiguous(), Lm, enc_for, row_groups).t().contiguous()
+        # every 16-row block's encoder call writes its code words straight into its column of `store`
+        zq = tldlq.ldlq_row_groups(ip.z.t().contiguous(), Lm, None, row_groups,
+                                   fused=lambda part, a, b: tldlq.ldlq_b200(part, Lm, K, codebook, packed=store[a // 16:b // 16])
+                                   ).t().contiguous()
         packed = store.reshape(-1, nw)
         w_hat = ip.restore(zq)
     rel = float(((w - w_hat) ** 2).mean() / w.square().mean())
@@ -132,8 +125,14 @@ def encode_matrix(w: torch.Tensor, K: int, codebook, seed: int, H: Optional[torc
 def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg", ldlq_filter: Callable[[str], bool] = is_mlp,
                  weight_fn: Callable = synthetic_weight, hessian_fn: Optional[Callable] = synthetic_hessian,
                  out_dir: Optional[str] = None, device=None, group=None, gather: bool = True,
-                 log: Optional[Callable[[dict], None]] = None, streams: int = 1, shard_dir: Optional[str] = None):
+                 log: Optional[Callable[[dict], None]] = None, streams: int = 1, shard_dir: Optional[str] = None,
+                 seed_fn: Callable[[str], int] = seed_of):
     """Encode this rank's share of the model; returns (results of this rank, gathered packed words on rank 0).
+
+    ``seed_fn(name)`` gives the incoherence-processing seed of a matrix.  The default, ``crc32(name)``, is what the
+    reference's model-level quantiser uses (``scripts/run_tcq_eval.py:115``); its packed exporter uses one seed for
+    every matrix, ``crc32(b"x")`` (``scripts/export_packed_8b.py:91,108``): pass ``lambda name: zlib.crc32(b"x")``
+    to reproduce that script's shards.
 
     ``results``: name -> {"tiles", "seconds", "weights_per_s", "rel_err", "ldlq", "skipped"}.
     ``streams`` > 1 keeps that many matrices in flight on this GPU (one host thread + CUDA stream each).
@@ -152,11 +151,34 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
     if shard_dir:
         os.makedirs(shard_dir, exist_ok=True)
 
+    cb_name = qtip.CODEBOOK_NAMES[qtip.codebook_id(codebook)]
+
+    def finished_earlier(name: str, path: Optional[str]):
+        """Packed words of ``name`` left by an earlier run with the SAME settings, else None (then it is encoded again).
+
+        A matrix counts as finished only if its words have this run's shape, its side-car names this run's K, codebook,
+        seed and LDLQ choice, and (with ``shard_dir``) its shard is there too; anything else is stale."""
+        if not path or not os.path.exists(path) or not os.path.exists(path + ".json"):
+            return None
+        n_out, k_in = shapes[name]
+        try:
+            meta = json.load(open(path + ".json"))
+            arr = np.load(path)
+        except Exception:
+            return None
+        want = {"K": K, "codebook": cb_name, "shape": [n_out, k_in], "seed": int(seed_fn(name)), "ldlq": name in ldlq_names}
+        if meta != want or arr.dtype != np.int32 or arr.shape != ((n_out // 16) * (k_in // 16), qtip.T_SEQ * K // 32):
+            return None
+        if shard_dir and not shards.shard_done(os.path.join(shard_dir, name + ".bin")):
+            return None
+        return arr
+
     def one(name: str, stream) -> None:
         n_out, k_in = shapes[name]
         path = os.path.join(out_dir, name + ".bits.npy") if out_dir else None
-        if path and os.path.exists(path):                       # resume: finished in an earlier run
-            packed_out[name] = torch.from_numpy(np.load(path)).to(dev)
+        old = finished_earlier(name, path)
+        if old is not None:                                     # resume: finished in an earlier run
+            packed_out[name] = torch.from_numpy(old).to(dev)
             results[name] = {"tiles": packed_out[name].shape[0], "skipped": True}
             return
         use_ldlq = name in ldlq_names
@@ -164,8 +186,10 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
         H = hessian_fn(name, k_in, dev) if use_ldlq else None
         stream.synchronize()
         t0 = time.perf_counter()
-        packed, _, rel, ip = encode_matrix(w, K, codebook, seed_of(name), H, return_ip=True)
-        stream.synchronize()
+        packed, _, rel, ip = encode_matrix(w, K, codebook, seed_fn(name), H, return_ip=True)
+        # synchronises, and raises if a bounded in-kernel wait gave up or a weight was not finite: such codes
+        # must not reach a shard or the gather
+        qtip.workspace_status(n_out // 16 if use_ldlq else (n_out // 16) * (k_in // 16), K, dev)
         dt = time.perf_counter() - t0
         if shard_dir:
             sh = shards.Shard(os.path.join(shard_dir, name + ".bin"))
@@ -179,6 +203,9 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
             tmp = path + ".tmp.npy"
             np.save(tmp, packed.cpu().numpy())
             os.replace(tmp, path)
+            with open(path + ".json.tmp", "w") as f:            # written last: its presence marks the matrix as finished
+                json.dump({"K": K, "codebook": cb_name, "shape": [n_out, k_in], "seed": int(seed_fn(name)), "ldlq": use_ldlq}, f)
+            os.replace(path + ".json.tmp", path + ".json")
         if log:
             log(rec)
 
@@ -212,6 +239,7 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
                                 errors.append(e)
                             break
                 s.synchronize()
+                qtip.release_workspace(dev, s)          # the stream dies with this thread; so does its scratch
 
         threads = [threading.Thread(target=worker, name=f"encode-stream-{i}") for i in range(min(streams, max(1, len(todo))))]
         for t in threads:

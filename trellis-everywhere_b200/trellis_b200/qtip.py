@@ -24,6 +24,7 @@ extension and a GPU; there is no CPU implementation and no other backend.
 """
 from __future__ import annotations
 
+import threading
 import weakref
 from typing import NamedTuple, Optional, Union
 
@@ -64,18 +65,37 @@ def _to_dev(t: torch.Tensor, dev: torch.device, dtype: torch.dtype) -> torch.Ten
 
 
 _workspaces: dict = {}
+_workspaces_lock = threading.Lock()
 
 
 def _workspace(dev: torch.device, n_tiles: int, K: int) -> torch.Tensor:
-    """Grow-only scratch per (device, stream): backpointers and per-tile hand-off words."""
+    """Grow-only scratch per (device, stream): backpointers and per-tile hand-off words.
+
+    Kernels of one stream run one after another, so a stream's calls can share one block; calls on
+    different streams may overlap and get different blocks.  Code that creates streams of its own
+    (``ldlq.ldlq_row_groups``, ``model.encode_model``) hands the block back with
+    ``release_workspace`` when its stream is done, otherwise every short-lived stream would keep
+    gigabytes alive.
+    """
     need = int(_lib.lib().tcq_workspace_bytes(n_tiles, K))
     key = (dev.index, _stream(dev))
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < need:
-        _workspaces[key] = None          # drop the old block before asking for a larger one
-        ws = torch.empty(need, dtype=torch.uint8, device=dev)
-        _workspaces[key] = ws
+    with _workspaces_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            _workspaces[key] = None          # drop the old block before asking for a larger one
+            ws = torch.empty(need, dtype=torch.uint8, device=dev)
+            _workspaces[key] = ws
     return ws
+
+
+def release_workspace(dev: torch.device, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Free the scratch block cached for ``stream`` (default: the current stream) of ``dev``.
+
+    Call it after the stream's work has finished (the block goes back to the allocator at once).
+    """
+    handle = stream.cuda_stream if stream is not None else _stream(dev)
+    with _workspaces_lock:
+        _workspaces.pop((dev.index, handle), None)
 
 
 def workspace_status(n_tiles: int, K: int, device=None) -> None:
@@ -92,8 +112,9 @@ def workspace_status(n_tiles: int, K: int, device=None) -> None:
 
 
 def release_workspaces() -> None:
-    """Free the cached scratch buffers."""
-    _workspaces.clear()
+    """Free the cached scratch buffers of every stream."""
+    with _workspaces_lock:
+        _workspaces.clear()
 
 
 # --------------------------------------------------------------------------- codebooks
@@ -177,6 +198,53 @@ def _encode_device(wd: torch.Tensor, K: int, cid: int, packed, dq, sse, bits) ->
                                       sse.data_ptr() if sse is not None else None,
                                       ws.data_ptr(), ws.numel(), _stream(dev))
     _lib.check(rc, "tcq_encode_tb")
+
+
+@torch.no_grad()
+def encode_rows(src: torch.Tensor, comp: Optional[torch.Tensor], K: int, codebook: CodebookLike, wq: torch.Tensor,
+                err: Optional[torch.Tensor] = None, packed: Optional[torch.Tensor] = None,
+                sse: Optional[torch.Tensor] = None) -> None:
+    """Encode one LDLQ row block where it lies: the ``enc`` step of ldlq.py:136-143 without its copies.
+
+    ``src`` is a ``(16, n_out)`` slice of the transposed matrix (rows = 16 consecutive input channels; any row
+    stride, unit column stride), ``comp`` the feedback owed to it (same strides) or None.  The block
+    ``src + comp`` is cut into ``n_out/16`` tiles (tile i = columns 16i..16i+15, t = (col % 16) * 16 + row),
+    encoded, and written back in the same layout: ``wq`` the reconstruction, ``err = src - wq``.
+    ``packed``: int32 view ``[n_out/16, 8K]`` whose rows may be strided (a column of the matrix's
+    ``[n_out/16, k_in/16, 8K]`` code array).  All tensors on one CUDA device; nothing synchronises.
+    """
+    if src.dim() != 2 or src.shape[0] != 16 or src.shape[1] % 16:
+        raise ValueError(f"expected a (16, n_out) block with n_out % 16 == 0, got {tuple(src.shape)}")
+    if K not in (2, 3, 4):
+        raise ValueError("K must be 2, 3 or 4")
+    cid = codebook_id(codebook)
+    if not src.is_cuda:
+        raise ValueError("encode_rows works on CUDA tensors only")
+    dev = src.device
+    n_out = src.shape[1]
+    ld = src.stride(0)
+    for name, t in (("src", src), ("comp", comp), ("wq", wq), ("err", err)):
+        if t is None:
+            continue
+        if t.dtype != torch.float32 or t.device != dev or tuple(t.shape) != (16, n_out) or t.stride(1) != 1 or t.stride(0) != ld:
+            raise ValueError(f"{name} must be a float32 (16, {n_out}) block on {dev} with the strides of src")
+    nw = T_SEQ * K // 32
+    pstride = 0
+    if packed is not None:
+        if packed.dtype != torch.int32 or packed.device != dev or tuple(packed.shape) != (n_out // 16, nw) or packed.stride(1) != 1:
+            raise ValueError(f"packed must be an int32 [{n_out // 16}, {nw}] view on {dev} with contiguous rows")
+        pstride = packed.stride(0) if n_out > 16 else nw
+    if sse is not None and (sse.dtype != torch.float32 or sse.device != dev or tuple(sse.shape) != (n_out // 16,) or not sse.is_contiguous()):
+        raise ValueError("sse must be a contiguous float32 [n_out/16] tensor")
+    if n_out == 0:
+        return
+    ws = _workspace(dev, n_out // 16, K)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tcq_encode_tb_rows(src.data_ptr(), comp.data_ptr() if comp is not None else None, ld, n_out, K, cid,
+                                           packed.data_ptr() if packed is not None else None, pstride, wq.data_ptr(),
+                                           err.data_ptr() if err is not None else None,
+                                           sse.data_ptr() if sse is not None else None, ws.data_ptr(), ws.numel(), _stream(dev))
+    _lib.check(rc, "tcq_encode_tb_rows")
 
 
 _HOST_CHUNK = 2 * 3552          # tiles per pipelined chunk of a host-tensor encode (two workspace chunks)
