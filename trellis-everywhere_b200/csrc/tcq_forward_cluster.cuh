@@ -79,15 +79,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
 // and stops exchanging metrics, so a counting bug shows up as an error status and invalid codes,
 // never as a hang.  (No suspend-time hint on the poll: a hint makes every unsatisfied poll sleep
 // for about that long, which cost 7 % of the kernel's throughput.)
+//
+// `gave_up` is a word in this CTA's shared memory, zero at launch.  The first wait that runs out
+// sets it, and from then on no wait of this CTA spins: each polls twice and reports failure, so a
+// launch whose protocol broke ends after about one time limit, not one per remaining wait.  The
+// flag is looked at on the slow path only and lives in shared memory on purpose: the step loop sits
+// at the register limit, and any extra state carried through its fast path (tried: a predicate, a
+// second return value) cost 6-7 % of the kernel's throughput.
 constexpr long long kMbarWaitCycles = 500000000LL;
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile unsigned int* gave_up) {
     if (mbar_try_wait(mbar, parity)) return true;
     const long long t0 = clock64();
-    while (clock64() - t0 < kMbarWaitCycles)
+    const long long limit = *gave_up ? 0 : kMbarWaitCycles;
+    while (clock64() - t0 < limit)
         if (mbar_try_wait(mbar, parity)) return true;
     // One more poll after the deadline: a thread that was descheduled across it (time slicing, an attached
     // profiler) must not report a phase that completed meanwhile as lost.
-    return mbar_try_wait(mbar, parity);
+    if (mbar_try_wait(mbar, parity)) return true;
+    *gave_up = 1u;
+    return false;
 }
 __device__ __forceinline__ void st_async_v4(uint32_t dst, float x, float y, float z, float w, uint32_t mbar) {
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
@@ -133,6 +143,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     float* const wv = reinterpret_cast<float*>(stage + size_t(2) * G * ROWBC);        // [G][256]
     unsigned long long* const red = reinterpret_cast<unsigned long long*>(wv + G * kT);   // [32] reduction scratch
     unsigned long long* const mbar = red + 32;     // [2 sets][2 buffers] mbarriers counting the bytes of each metric buffer
+    volatile unsigned int* const gave_up = reinterpret_cast<volatile unsigned int*>(red + 40);   // set by the first wait that runs out
 
     const int tid = threadIdx.x;
     const bool constrained = a.overlap != nullptr;
@@ -212,11 +223,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // inflates exactly that one, so that its timeouts happen after the last store has landed.)
     auto wait_buffer = [&](int s, int b, bool last) {
         const uint32_t m = smem_u32(mbar + (2 * s + b));
-        // Fast path first; a thread that has already given up once polls once and never spins again, so a
-        // launch whose protocol broke still finishes in about one time limit, not one per wait.
-        if (!mbar_try_wait(m, (parity >> (2 * s + b)) & 1u)) {
-            if (timed_out || !mbar_wait(m, (parity >> (2 * s + b)) & 1u)) timed_out = true;
-        }
+        if (!mbar_wait(m, (parity >> (2 * s + b)) & 1u, gave_up)) timed_out = true;
         parity ^= 1u << (2 * s + b);
         if (tid == 0 && !timed_out) mbar_expect(m, kBufBytes + (last ? uint32_t(a.inject_extra_bytes) : 0u));
     };
@@ -306,6 +313,7 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
 #pragma unroll
         for (int i = 0; i < 4; ++i) mbar_init(smem_u32(mbar + i), 1);
         mbar_fence_init();
+        *gave_up = 0u;
     }
     cluster.sync();                      // every CTA's mbarriers exist before anyone can signal them
     if (tid == 0) {

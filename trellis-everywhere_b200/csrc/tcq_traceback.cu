@@ -11,9 +11,10 @@
 // Whatever q_t turns out to be, e_{t-1} is one of only Q edges that share the low
 // bits e_t >> K, so lane j < Q fetches row t-1's entry for candidate q = j while
 // the row-t load is still in flight, and the pick is a shuffle; one row further
-// back there are Q*Q possible edges, fetched the same way.  The dependent chain is
-// thus one memory round trip per three steps (two at K = 4).  Afterwards the 32
-// lanes turn the 256 states held in shared memory into coalesced outputs.
+// back there are Q*Q possible edges, which can be fetched the same way.  The
+// dependent chain is thus one memory round trip per two (or three) steps.
+// Afterwards the 32 lanes turn the 256 states held in shared memory into coalesced
+// outputs.
 #include "tcq_traceback.cuh"
 
 namespace tcq {
@@ -35,7 +36,7 @@ __device__ __forceinline__ uint32_t bp_entry(const unsigned char* row, uint32_t 
     return (v >> (bit & 7)) & (Q - 1);
 }
 
-template <int K>
+template <int K, int DEPTH>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const TracebackArgs a) {
     using GE = Geo<K>;
     constexpr uint32_t Q = GE::Q, E = GE::E, ROWB = GE::ROWB, NW = GE::NWORDS;
@@ -66,8 +67,10 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) tcq_traceback_kernel(const 
     // ---- the walk: DEPTH rows per memory round trip ----
     // Row r's entry is one broadcast load.  Row r-1's entry can only sit at one of Q edges ((j1 << HB) | (e >> K)),
     // row r-2's at one of Q*Q ((j2 << HB) | (j1 << (HB-K)) | (e >> 2K)); lanes fetch all of them at once and the
-    // picks are shuffles.  (Q*Q = 256 candidates at K = 4 would be 8 loads per lane: two rows per trip there.)
-    constexpr int DEPTH = (K == 4) ? 2 : 3;
+    // picks are shuffles.  DEPTH = 3 shortens the dependent chain by a third but every trip then waits for the
+    // slowest of 1 + Q + Q*Q scattered sectors instead of 1 + Q; measured, it pays only at K = 2 (16 candidates)
+    // and only for small batches, where the walk is bound by latency rather than by sector traffic.
+    static_assert(DEPTH == 2 || DEPTH == 3, "two or three rows per trip");
     constexpr int PER = 32 / int(Q) > 0 ? 32 / int(Q) : 1;      // level-2 candidates j2 covered by one load per lane
     constexpr int NL2 = (int(Q) + PER - 1) / PER;              // level-2 loads per lane
     int r = a.bp_steps - 1;
@@ -153,9 +156,12 @@ cudaError_t launch_traceback(int K, const TracebackArgs& a, cudaStream_t stream)
     if (a.n <= 0) return cudaSuccess;
     const unsigned grid = unsigned((a.n + kWarpsPerCta - 1) / kWarpsPerCta);
     switch (K) {
-        case 2: tcq_traceback_kernel<2><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
-        case 3: tcq_traceback_kernel<3><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
-        case 4: tcq_traceback_kernel<4><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
+        case 2:
+            if (a.n <= 1024) tcq_traceback_kernel<2, 3><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
+            else tcq_traceback_kernel<2, 2><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
+            break;
+        case 3: tcq_traceback_kernel<3, 2><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
+        case 4: tcq_traceback_kernel<4, 2><<<grid, kWarpsPerCta * 32, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
