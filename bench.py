@@ -340,9 +340,12 @@ def measure_model_encode(torch, dist, args, world: int, rank: int, dev) -> dict:
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    results, gathered = model.encode_model(shapes, K_BITS, "mcg", device=dev, log=recs.append, streams=args.model_streams)
+    results, own = model.encode_model(shapes, K_BITS, "mcg", device=dev, log=recs.append, streams=args.model_streams, gather=False)
     torch.cuda.synchronize(dev)
-    busy = time.perf_counter() - t0                           # this rank: its matrices + its part of the gather
+    busy = time.perf_counter() - t0                           # this rank's own matrices, before it waits for anyone
+    ldlq_names = [n for n in shapes if model.is_mlp(n)]
+    gathered = model.gather_model_codes(shapes, ldlq_names, own, K_BITS, world, rank, dev)
+    torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
     wall = time.perf_counter() - t0
@@ -364,6 +367,7 @@ def measure_model_encode(torch, dist, args, world: int, rank: int, dev) -> dict:
                     "whole matrices placed longest-first, packed codes gathered to rank 0; includes weight and Hessian synthesis",
             "seconds": wall, "weights_per_s": total / wall, "matrices": len(shapes), "weights": total,
             "rank_busy_seconds": busy_all, "imbalance_max_over_mean": max(busy_all) / (sum(busy_all) / len(busy_all)),
+            "gather_and_wait_seconds": wall - max(busy_all),
             "matrix_seconds_ldlq": [float(x[1]) for x in allst], "matrix_seconds_plain": [float(x[2]) for x in allst],
             "matrices_per_rank": [int(x[3]) for x in allst],
             "gathered_matrices": len(gathered) if gathered is not None else 0,
@@ -628,6 +632,74 @@ def run_decode_matvec(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args) -> None:
+    """Side measurement of the packed decode kernel (codes -> reconstruction): 4 bytes written + K/8 read per weight.
+
+    262 144 tiles of random code words (every bit pattern is a valid stream): 256 MiB of output, larger than L2, so
+    back-to-back launches run at DRAM speed.  ``e2e`` copies the packed words from pinned host memory and the
+    reconstruction back inside the timing."""
+    import numpy as np
+    import torch
+    from trellis_b200 import _lib, qtip
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n = args.tiles or 262144
+    nw = 8 * K_BITS
+    g = torch.Generator(device=dev).manual_seed(0)
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, nw), dtype=torch.int32, device=dev, generator=g)
+    dq = torch.empty((n, T_SEQ), dtype=torch.float32, device=dev)
+    L = _lib.lib()
+    cid = qtip.CODEBOOK_IDS[CODEBOOK]
+    st = torch.cuda.current_stream().cuda_stream
+    ph = packed.cpu().pin_memory()
+    dh = torch.empty((n, T_SEQ), dtype=torch.float32, pin_memory=True)
+
+    def step_device():
+        _lib.check(L.tcq_decode_packed(packed.data_ptr(), n, K_BITS, cid, dq.data_ptr(), st), "tcq_decode_packed")
+
+    def step_host():
+        dh.copy_(qtip.decode_packed(ph.to(dev, non_blocking=True), K_BITS, cid), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, reps):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    with ClockSampler(0) as clocks:
+        ms = timed(step_device, max(args.steps, 20))
+        ms_host = timed(step_host, args.steps)
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            step_device()
+        torch.cuda.synchronize()
+    from oracle import oracle as O
+    O.build()
+    want = O.decode_packed(packed[:64].cpu().numpy().view(np.uint32), K_BITS, CODEBOOK)
+    ok = bool(np.array_equal(dq[:64].cpu().numpy().view(np.uint32), want.view(np.uint32)))
+    hbm = measured_peaks().get("hbm_gbs") or 6650.0
+    byt = n * T_SEQ * 4 + n * nw * 4
+    gbs = byt / (ms * 1e-3) / 1e9
+    line = {"metric": f"weights decoded/sec (packed decode, L=16, K={K_BITS})", "value": n * T_SEQ / (ms * 1e-3), "unit": "weights/s",
+            "n_gpus": 1, "steps": max(args.steps, 20), "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"SIDE MEASUREMENT: packed decode of {n} tiles, K={K_BITS}, {CODEBOOK}; {n * T_SEQ * 4 / 2 ** 20:.0f} MiB out "
+                                   "(larger than L2, no flush needed)", "tiles": n},
+            "e2e": {"value": n * T_SEQ / (ms_host * 1e-3), "unit": "weights/s", "h2d_bytes_per_step": n * nw * 4, "d2h_bytes_per_step": n * T_SEQ * 4},
+            "gpu_launches": max(args.steps, 20),
+            "roofline": {"bound": "hbm", "kernel": f"tcq_decode_packed_kernel<K={K_BITS}, {CODEBOOK}>", "achieved": gbs, "peak": hbm, "unit": "GB/s",
+                         "frac": gbs / hbm, "traffic": None, "algorithmic": "4 B written + K/8 B read per weight"},
+            "parity": {"tiles": 64, "dq_equal": ok, "against": "CPU oracle window decode, bit for bit"}, "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def run_ip(args) -> None:
     """Side measurement of the incoherence-processing kernels (the producer of the encoder's tiles and the consumer of
     its reconstruction) through the C ABI with preallocated buffers: forward = 20 algorithmic bytes per weight (w read
@@ -706,9 +778,9 @@ def main() -> None:
                     help="bits per weight; anything but the default 3 is a side measurement, not the benchmark")
     ap.add_argument("--codebook", default="3inst", choices=("1mad", "3inst", "mcg"),
                     help="codebook; anything but the default 3inst is a side measurement, not the benchmark")
-    ap.add_argument("--path", choices=("encode", "decode_matvec", "ip"), default="encode",
-                    help="encode = the benchmark; decode_matvec / ip = side measurements of the packed format's consumer kernel "
-                         "and of the incoherence-processing kernels")
+    ap.add_argument("--path", choices=("encode", "decode", "decode_matvec", "ip"), default="encode",
+                    help="encode = the benchmark; decode / decode_matvec / ip = side measurements of the packed decode kernel, the "
+                         "packed format's consumer kernel and the incoherence-processing kernels")
     ap.add_argument("--n-out", type=int, default=151936, help="decode_matvec: output rows (default: lm_head of the model shape)")
     ap.add_argument("--k-in", type=int, default=4096, help="decode_matvec: input columns")
     ap.add_argument("--m", type=int, default=1, help="decode_matvec: right-hand sides")
@@ -725,7 +797,7 @@ def main() -> None:
         if args.impl != "b200" or args.gpus != 1:
             raise SystemExit(f"--path {args.path} is a one-GPU side measurement of this library")
         if rank == 0:
-            (run_decode_matvec if args.path == "decode_matvec" else run_ip)(args)
+            {"decode_matvec": run_decode_matvec, "decode": run_decode, "ip": run_ip}[args.path](args)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     elif args.impl == "reference-triton":

@@ -189,17 +189,24 @@ __global__ void __launch_bounds__(NT, 1) tcq_forward_cluster_kernel(const Cluste
     // (coalesced 128-bit stores).  A set's slices are GS * ROWBC / 16 <= NT words, one per thread; which word, which
     // tile of the set and the byte offset from the set's first row are fixed for the launch.
     constexpr int V = ROWBC / 16;
-    static_assert(GS * V <= NT, "one 128-bit word of a set's row slices per thread");
-    const int fl_gg = tid / V;
-    const bool fl_on = tid < GS * V;
-    const size_t fl_off = size_t(fl_gg) * a.bp_steps * ROWB + size_t(rank) * ROWBC + size_t(tid - fl_gg * V) * 16;
+    constexpr int FW = (GS * V + NT - 1) / NT;     // 128-bit words of a set's row slices per thread
+    int fl_src[FW];
+    size_t fl_off[FW];
+    int fl_gg[FW];
+#pragma unroll
+    for (int k = 0; k < FW; ++k) {
+        const int wd = tid + k * NT;
+        fl_src[k] = wd;
+        fl_gg[k] = wd < GS * V ? wd / V : -1;
+        fl_off[k] = size_t(wd / V) * a.bp_steps * ROWB + size_t(rank) * ROWBC + size_t(wd % V) * 16;
+    }
     auto flush_set = [&](int s, int t, int buf, long long tile0) {
         if (t < t_store0) return;
-        if (fl_on && tile0 + s * GS + fl_gg < a.n) {
-            const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(buf) * G * ROWBC + size_t(s) * GS * ROWBC);
-            unsigned char* row0 = a.bp + (size_t(tile0 + s * GS) * a.bp_steps + (t - t_store0)) * ROWB;     // uniform
-            *reinterpret_cast<uint4*>(row0 + fl_off) = src[tid];
-        }
+        const uint4* src = reinterpret_cast<const uint4*>(stage + size_t(buf) * G * ROWBC + size_t(s) * GS * ROWBC);
+        unsigned char* row0 = a.bp + (size_t(tile0 + s * GS) * a.bp_steps + (t - t_store0)) * ROWB;     // uniform
+#pragma unroll
+        for (int k = 0; k < FW; ++k)
+            if (fl_gg[k] >= 0 && tile0 + s * GS + fl_gg[k] < a.n) *reinterpret_cast<uint4*>(row0 + fl_off[k]) = src[fl_src[k]];
     };
 
     constexpr uint32_t kBufBytes = uint32_t(GS) * EC * 4;     // bytes every (set, buffer) receives per step

@@ -9,7 +9,8 @@ constexpr int kLU = 8;       // successors per work item, single-CTA kernel
 constexpr int kGMax = 3;     // most tiles one CTA advances together (shared-memory bound)
 constexpr int kCLU4 = 4;     // successors per work item with 4 CTAs per cluster (32 codebook values per thread)
 constexpr int kCLU2 = 4;     // ... with 2 CTAs per cluster (64 codebook values per thread, two items of four successors; one item of
-                             //     eight was measured 8 % slower: it spills at the 128-register limit)
+                             //     eight was measured 8 % slower: it spills at the 128-register limit; 256 threads
+                             //     with 128 values each, 226-231 registers, 11-21 % slower: too few warps to hide latencies)
 
 template <int CB>
 cudaError_t launch_cb(const ForwardArgs& a, unsigned long long* keys, int num_sms, cudaStream_t stream, int* nkeys) {

@@ -129,6 +129,8 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
                  seed_fn: Callable[[str], int] = seed_of):
     """Encode this rank's share of the model; returns (results of this rank, gathered packed words on rank 0).
 
+    With ``gather=False`` the second value is this rank's own ``name -> packed words`` instead, and no collective runs.
+
     ``seed_fn(name)`` gives the incoherence-processing seed of a matrix.  The default, ``crc32(name)``, is what the
     reference's model-level quantiser uses (``scripts/run_tcq_eval.py:115``); its packed exporter uses one seed for
     every matrix, ``crc32(b"x")`` (``scripts/export_packed_8b.py:91,108``): pass ``lambda name: zlib.crc32(b"x")``
@@ -248,10 +250,9 @@ def encode_model(shapes: Dict[str, Tuple[int, int]], K: int = 3, codebook="mcg",
             t.join()
         if errors:
             raise errors[0]
-    gathered = None
-    if gather:
-        gathered = gather_model_codes(shapes, ldlq_names, packed_out, K, world, rank, dev, group)
-    return results, gathered
+    if not gather:
+        return results, packed_out          # this rank's own matrices; ``gather_model_codes`` can collect them later
+    return results, gather_model_codes(shapes, ldlq_names, packed_out, K, world, rank, dev, group)
 
 
 def gather_model_codes(shapes, ldlq_names: Sequence[str], packed_out: Dict[str, torch.Tensor], K: int, world: int,
