@@ -84,6 +84,40 @@ def test_row_block_entry_point_equals_the_tile_entry_point(mods, oracle, luts, K
         q.encode_rows(src, comp.contiguous(), K, name, wq2)              # strides differ from src
 
 
+def test_row_block_entry_point_with_a_small_workspace_and_bad_arguments(mods):
+    """Through the C ABI directly: a workspace of a few tiles makes the row block go through several chunks (each
+    chunk starts 16 columns further into the block per tile); argument errors are refused before anything is launched."""
+    q, l = mods
+    L = q._lib.lib()
+    torch.manual_seed(12)
+    n_out, ld = 23 * 16, 23 * 16 + 8
+    src = torch.randn(16, ld, device="cuda")
+    comp = torch.randn(16, ld, device="cuda") * 0.05
+    wq, err = torch.zeros_like(src), torch.zeros_like(src)
+    packed = torch.zeros(23, 24, dtype=torch.int32, device="cuda")
+    sse = torch.zeros(23, device="cuda")
+    ws = torch.empty(int(L.tcq_workspace_min_bytes(3)) * 5 + 4096, dtype=torch.uint8, device="cuda")      # ~5-tile chunks
+    st = torch.cuda.current_stream().cuda_stream
+    args = [src.data_ptr(), comp.data_ptr(), ld, n_out, 3, 2, packed.data_ptr(), 24, wq.data_ptr(), err.data_ptr(),
+            sse.data_ptr(), ws.data_ptr(), ws.numel(), st]
+    assert L.tcq_encode_tb_rows(*args) == 0
+    ref = q.encode(l.rows_to_tiles(src[:, :n_out] + comp[:, :n_out]), 3, "mcg")
+    assert torch.equal(packed, ref.packed) and torch.equal(sse, ref.sse)
+    assert torch.equal(wq[:, :n_out], l.tiles_to_rows(ref.dq, n_out)) and torch.equal(err[:, :n_out], src[:, :n_out] - wq[:, :n_out])
+    assert bool((wq[:, n_out:] == 0).all())
+
+    def call(**kw):
+        a = list(args)
+        for k, v in kw.items():
+            a[{"src": 0, "ld": 2, "n_out": 3, "K": 4, "pstride": 7, "wq": 8, "ws_bytes": 12}[k]] = v
+        return L.tcq_encode_tb_rows(*a)
+
+    assert call(n_out=n_out + 8) == -8 and call(ld=n_out - 16) == -8 and call(pstride=23) == -8       # shape / strides
+    assert call(K=5) == -1 and call(src=None) == -4 and call(wq=None) == -4 and call(ws_bytes=1024) == -6
+    assert call(n_out=0) == 0
+    torch.cuda.synchronize()
+
+
 def test_fused_recursion_equals_the_general_recursion(mods, golden):
     """ldlq_b200 (encoder step in place) against ldlq(..., make_enc) (the reference's structure, ldlq.py:72-99 and
     136-143): same arithmetic in the same order, so reconstruction and packed words are identical."""
