@@ -335,6 +335,13 @@ def measure_model_encode(torch, dist, args, world: int, rank: int, dev) -> dict:
     """A fixed slice of the Qwen3-8B-shaped model through ``model.encode_model`` (strong scaling over the ranks)."""
     from trellis_b200 import model
     shapes = model.qwen3_8b_shapes(layers=args.model_layers)
+    # Warm-up, untimed: a two-matrix model of small shapes through the same code (one plain, one LDLQ matrix per rank and
+    # the gather), so that one-time costs are not billed to the measurement: cuSOLVER / cuBLAS handles of the block-LDL
+    # step, the library's kernel images, NCCL's point-to-point connections for the gather (about a second per rank
+    # together, the same at every N, which would read as a scaling loss at N = 8 where the measurement takes six).
+    warm = {f"model.layers.{i}.{m}": s for i in range(world) for m, s in (("self_attn.k_proj", (64, 256)), ("mlp.down_proj", (64, 256)))}
+    model.encode_model(warm, K_BITS, "mcg", device=dev, streams=args.model_streams,
+                       hessian_fn=lambda name, k, d: model.synthetic_hessian(name, k, d, rows=512))
     recs = []
     torch.cuda.synchronize(dev)
     if world > 1:

@@ -431,7 +431,7 @@ def test_workspace_status_and_bounded_wait_selftest(q):
     assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == -10          # TCQ_E_DEVICE_TIMEOUT
     # a thread gives up once (about a quarter of a second) and never spins again: the launch must not take a
     # time limit per wait
-    assert time.perf_counter() - t0 < 1.5
+    assert time.perf_counter() - t0 < 1.0
     again = torch.empty_like(packed)
     assert L.tcq_encode_tb(w.data_ptr(), 8, 3, 2, again.data_ptr(), None, None, None, ws.data_ptr(), ws.numel(), s) == 0
     assert L.tcq_workspace_status(ws.data_ptr(), ws.numel(), 8, 3, s) == 0
