@@ -165,6 +165,7 @@ __device__ __forceinline__ void take_if_equal_fma(float& tag, float c, float bes
 }
 // Q = candidates per successor.  With 8 or fewer, every other move is a select; with 16 the compare/select
 // pipe is the busier one and only every fourth move stays there (measured: +1.4 % at K = 4, -0.5 % at K = 3).
+// (At Q = 8, other splits were measured against 3 selects + 4 fmas: 2 + 5 -0.3 %, 1 + 6 -1.6 %, 0 + 7 -2.1 %, 5 + 2 -3.0 %.)
 template <int Q>
 __device__ __forceinline__ void take_if_equal_balanced(int q, float& tag, float c, float best, float zero, float value) {
     const bool on_select_pipe = Q >= 16 ? (q & 3) == 1 : (q & 1) != 0;
