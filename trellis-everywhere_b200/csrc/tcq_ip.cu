@@ -159,15 +159,26 @@ __global__ void __launch_bounds__(kRowThreads) ip_had_rows_kernel(const float* _
 // lane, the others through warp shuffles.  No shared memory, no barriers.
 //   forward: in = z1 (row-major), v = z1 * cs[c] with cs = 1/in_s;  out = v * (1/scale), in tile order or row-major
 //   inverse: in = zq (tile order or row-major), v = zq * scale;  out = v * cs[c] with cs = in_s, row-major
+// Forward: a CTA of 16 warps takes 16 consecutive rows (n is a multiple of 16) and one 128-column chunk, so that in
+// tile order it writes eight whole tiles, 8 KiB contiguous (3 % faster than rows spread over CTAs).  Inverse: eight
+// warps per CTA walk the (row, chunk) pairs in row-major order (the 16-row form was 1 % slower there).
+constexpr int kColThreadsFwd = 512;
+
 template <bool INV>
-__global__ void __launch_bounds__(kIpThreads) ip_had_cols_kernel(const float* __restrict__ in, long long n, long long k, int logB,
-                                                                float norm, const float* __restrict__ in_s,
-                                                                const float* __restrict__ scale, int tiled,
-                                                                float* __restrict__ out) {
+__global__ void __launch_bounds__(INV ? kIpThreads : kColThreadsFwd)
+ip_had_cols_kernel(const float* __restrict__ in, long long n, long long k, int logB, float norm, const float* __restrict__ in_s,
+                   const float* __restrict__ scale, int tiled, float* __restrict__ out) {
     const int lane = threadIdx.x & 31;
-    const long long chunks = (k + 127) / 128;
-    const long long gw = (long long)blockIdx.x * (kIpThreads / 32) + (threadIdx.x >> 5);
-    const long long r = gw / chunks, c = (gw - r * chunks) * 128 + lane * 4;
+    long long r, c;
+    if constexpr (INV) {
+        const long long chunks = (k + 127) / 128;
+        const long long gw = (long long)blockIdx.x * (kIpThreads / 32) + (threadIdx.x >> 5);
+        r = gw / chunks;
+        c = (gw - r * chunks) * 128 + lane * 4;
+    } else {
+        r = (long long)blockIdx.y * 16 + (threadIdx.x >> 5);
+        c = (long long)blockIdx.x * 128 + lane * 4;
+    }
     if (r >= n) return;                                       // whole warps leave together
     const bool live = c < k;                                  // k is a multiple of 16: a lane's four columns are all in or all out
     const long long rowmajor = r * k + c;
@@ -259,9 +270,8 @@ cudaError_t launch_ip_forward(const float* w, long long n, long long k, const fl
     if (err != cudaSuccess) return err;
     ip_sum_parts_kernel<<<unsigned((k + kIpThreads - 1) / kIpThreads), kIpThreads, 0, stream>>>(wk.colpart, int(n / B0), k, wk.colsum);
     ip_finish_scales_kernel<<<1, 1024, 0, stream>>>(wk.colsum, 1, k, float(n), in_s, wk.inv_in_s, float(n) * float(k), cb_rms, scale);
-    const long long warps = n * ((k + 127) / 128);
-    const unsigned g1 = unsigned((warps + kIpThreads / 32 - 1) / (kIpThreads / 32));
-    ip_had_cols_kernel<false><<<g1, kIpThreads, 0, stream>>>(wk.z1, n, k, ilog2(B1), float(1.0 / sqrt(double(B1))), wk.inv_in_s, scale, tiled, z_out);
+    const dim3 g1(unsigned((k + 127) / 128), unsigned(n / 16));
+    ip_had_cols_kernel<false><<<g1, kColThreadsFwd, 0, stream>>>(wk.z1, n, k, ilog2(B1), float(1.0 / sqrt(double(B1))), wk.inv_in_s, scale, tiled, z_out);
     return cudaGetLastError();
 }
 
