@@ -175,6 +175,19 @@ def test_ragged_tile_counts(q, oracle, luts, n):
         assert torch.equal(one_by_one, r.packed[n - m:])                # group size must not change results
 
 
+def test_large_k2_batch_against_oracle(q, oracle, luts):
+    """K = 2 walks three backpointer rows per memory round trip up to 1 024 tiles and two beyond: both forms against
+    the oracle on tiles spread over the batch."""
+    g = torch.Generator(device="cuda").manual_seed(77)
+    w = torch.randn(1500, 256, generator=g, device="cuda")
+    big = q.encode(w, 2, "3inst", want_bits=True)
+    small = q.encode(w[:900], 2, "3inst", want_bits=True)
+    assert torch.equal(big.packed[:900], small.packed) and torch.equal(big.dq[:900], small.dq)
+    idx = torch.arange(0, 1500, 125, device="cuda")
+    bits, dq, sse = oracle.viterbi_tb(_np(w[idx]), 2, luts["3inst"], with_sse=True)
+    assert np.array_equal(_np(big.bits[idx]), bits) and same_bits(_np(big.dq[idx]), dq) and same_bits(_np(big.sse[idx]), sse)
+
+
 def test_small_workspace_gives_same_codes(q):
     torch.manual_seed(5)
     w = torch.randn(40, 256, device="cuda")

@@ -388,3 +388,26 @@ def test_resume_ignores_stale_or_foreign_files(tmp_path):
             assert not r6["model.layers.0.self_attn.k_proj"]["skipped"]                          # no side-car: not trusted
     finally:
         model.encode_matrix, model.qtip.workspace_status, model.qtip.codebook_id = real
+
+
+def test_reference_staging_recipe(tmp_path, monkeypatch):
+    """oracle/make_ref.py: what it stages is byte-identical to the checkout (digest check), a tampered copy is not
+    accepted, and without a checkout it stages nothing.  Skipped where no checkout of the reference is at hand."""
+    import hashlib
+    import shutil
+    from oracle import make_ref
+    assert make_ref.stage(str(tmp_path / "no_such_checkout")) is None
+    src = os.path.join(make_ref.default_checkout(), "src", "trellis")
+    if not all(os.path.isfile(os.path.join(src, f)) for f in make_ref.FILES):
+        pytest.skip("no checkout of the reference here")
+    monkeypatch.setattr(make_ref, "REF_DIR", str(tmp_path / "_ref"))
+    assert make_ref.staged() is None
+    assert make_ref.stage() == str(tmp_path / "_ref") and make_ref.staged() == str(tmp_path / "_ref")
+    for f in make_ref.FILES:
+        a = hashlib.sha256(open(os.path.join(src, f), "rb").read()).hexdigest()
+        b = hashlib.sha256(open(os.path.join(tmp_path, "_ref", "trellis", f), "rb").read()).hexdigest()
+        assert a == b
+    with open(os.path.join(tmp_path, "_ref", "trellis", "qtip.py"), "a") as fh:
+        fh.write("# edited\n")
+    assert make_ref.staged() is None                       # a modified copy is not "the reference"
+    shutil.rmtree(tmp_path / "_ref")
