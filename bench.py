@@ -396,7 +396,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     lib = _lib.lib()
     cid = qtip.CODEBOOK_IDS[CODEBOOK]
 
-    torch.set_num_threads(host_threads())                # torchrun exports OMP_NUM_THREADS=1; the host-side build of the workload is a matmul
+    # torchrun exports OMP_NUM_THREADS=1; the host-side build of the workload is a few matmuls.  Every rank builds it at the
+    # same time, so each takes its share of the cores (all ranks asking for all cores makes the OpenMP teams fight).
+    torch.set_num_threads(max(1, host_threads() // max(world, 1)))
     host = workload_tiles_host(qtip.codebook_lut(CODEBOOK, "cpu")).pin_memory()
     if args.tiles:                                       # reduced case for profiler captures; not the benchmark
         host = host[:args.tiles].contiguous().pin_memory()
