@@ -109,6 +109,7 @@ TCQ_API int tcq_encode_tb(const float *w, int64_t n_tiles, int K, int codebook, 
  *   err     [16][ld] fp32 out: src - wq (the uncompensated error the recursion feeds back), or NULL
  *   sse     [n_out/16] fp32 out: squared error of each tile against src + comp, or NULL
  *   ws      as tcq_encode_tb, sized for n_out/16 tiles
+ * src and comp are only read; wq and err must not overlap them or each other.
  * Codes and reconstruction are bit-identical to tcq_encode_tb on the transposed copy.
  */
 TCQ_API int tcq_encode_tb_rows(const float *src, const float *comp, int64_t ld, int64_t n_out, int K, int codebook,
