@@ -564,7 +564,7 @@ def run_decode_matvec(args) -> None:
     from trellis_b200 import _lib, qtip
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    n_out, k_in, m = args.n_out, args.k_in, args.m
+    n_out, k_in, m = args.n_out or 151936, args.k_in or 4096, args.m
     tiles = (n_out // 16) * (k_in // 16)
     g = torch.Generator(device=dev).manual_seed(0)
     packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (tiles, 8 * K_BITS), dtype=torch.int32, device=dev, generator=g)
@@ -709,6 +709,76 @@ def run_decode(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_ldlq(args) -> None:
+    """Side measurement of the third benchmark configuration: LDLQ + TCQ of one 12288 -> 4096 (down_proj-shaped) matrix.
+
+    ``workloads.cfg3_case``: weights N(0, 0.02^2), proxy Hessian from 8 192 activation rows with log-uniform channel scales;
+    sigma_reg 0.025, 16-row blocks, 128-row spans (the reference's parameters), MCG, K bits.  One step = the whole matrix
+    through ``model.encode_matrix`` (incoherence processing, block LDL, the recursion with its k_in/16 strictly serial encoder
+    calls of n_out/16 tiles, restore); the recursion alone and one encoder call alone are timed beside it."""
+    import torch
+    from trellis_b200 import ldlq as L
+    from trellis_b200 import model, qtip, workloads
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n_out, k_in = args.n_out or 4096, args.k_in or 12288
+    w, H = workloads.cfg3_case(n_out, k_in, rows=8192, device=dev)
+    lut = qtip.codebook_lut("mcg", dev)
+
+    def whole(groups):
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        packed, w_hat, rel = model.encode_matrix(w, K_BITS, "mcg", 0, H, row_groups=groups)
+        torch.cuda.synchronize(dev)
+        return time.perf_counter() - t0, rel
+
+    with ClockSampler(0) as clocks:
+        whole(1)                                                      # warm-up: handles, kernel images, scratch
+        t_whole = min(whole(1)[0] for _ in range(max(1, args.steps // 2)))
+        t_groups, rel = whole(2)
+        t_groups = min(t_groups, whole(2)[0])
+        ip = qtip.IPContext(w, lut.square().mean().sqrt().item(), seed=0)
+        Lm = L.block_ldl(L.regularize_H(L._transform_H(H, ip.su, block=128), 0.025), b=16)
+        zt = ip.z.t().contiguous()
+        L.ldlq_b200(zt, Lm, K_BITS, "mcg")
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        L.ldlq_b200(zt, Lm, K_BITS, "mcg")
+        torch.cuda.synchronize(dev)
+        t_rec = time.perf_counter() - t0
+        rows, comp = zt[:16], torch.zeros_like(zt[:16])
+        wq, err = torch.empty_like(rows), torch.empty_like(rows)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        qtip.encode_rows(rows, comp, K_BITS, "mcg", wq, err)
+        a.record()
+        for _ in range(50):
+            qtip.encode_rows(rows, comp, K_BITS, "mcg", wq, err)
+        b.record()
+        torch.cuda.synchronize(dev)
+        call_ms = a.elapsed_time(b) / 50
+    weights = n_out * k_in
+    calls = k_in // 16
+    peaks = measured_peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    peak_lane_ops = sms * 128 * float(peaks.get("sm_max_mhz", 1965.0)) * 1e6
+    achieved = weights * STATE_EVALS_PER_WEIGHT * LANE_OPS_PER_EVAL / t_whole
+    print(json.dumps({
+        "metric": f"weights encoded/sec (LDLQ + TCQ, L=16, K={K_BITS})", "value": weights / t_whole, "unit": "weights/s", "n_gpus": 1,
+        "steps": max(1, args.steps // 2), "warmup": 1, "ms_per_step": t_whole * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"SIDE MEASUREMENT, config 3: LDLQ + TCQ of one {k_in} -> {n_out} fp32 matrix N(0,0.02^2), Hessian from 8192 "
+                               f"rows with log-uniform channel scales, sigma_reg 0.025, 16-row blocks, 128-row spans, MCG, K={K_BITS}",
+                   "n_out": n_out, "k_in": k_in, "encoder_calls": calls, "tiles_per_call": n_out // 16},
+        "recursion_only": {"seconds": t_rec, "weights_per_s": weights / t_rec},
+        "two_column_groups": {"seconds": t_groups, "weights_per_s": weights / t_groups},
+        "encoder_call": {"ms": call_ms, "calls_x_ms_seconds": calls * call_ms * 1e-3, "weights_per_s": (n_out // 16) * T_SEQ / (call_ms * 1e-3)},
+        "rel_err": rel, "gpu_launches": 4 * calls,
+        "roofline": {"bound": "alu", "kernel": "Viterbi step kernel at n_out/16 tiles per launch", "achieved": achieved / 1e12,
+                     "peak": peak_lane_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_lane_ops, "traffic": None,
+                     "note": "whole matrix incl. LDL, GEMMs and restore; a 256-tile launch fills 64 of the 74 two-SM clusters"},
+        "clocks": clocks.summary()}), flush=True)
+
+
 def run_ip(args) -> None:
     """Side measurement of the incoherence-processing kernels (the producer of the encoder's tiles and the consumer of
     its reconstruction) through the C ABI with preallocated buffers: forward = 20 algorithmic bytes per weight (w read
@@ -717,7 +787,7 @@ def run_ip(args) -> None:
     from trellis_b200 import _lib, qtip
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    n, k = args.n_out if args.n_out != 151936 else 12288, args.k_in
+    n, k = args.n_out or 12288, args.k_in or 4096
     g = torch.Generator(device=dev).manual_seed(0)
     w = torch.randn(n, k, device=dev, generator=g) * 0.02
     ip = qtip.IPContext(w, 0.9, seed=0)
@@ -787,11 +857,12 @@ def main() -> None:
                     help="bits per weight; anything but the default 3 is a side measurement, not the benchmark")
     ap.add_argument("--codebook", default="3inst", choices=("1mad", "3inst", "mcg"),
                     help="codebook; anything but the default 3inst is a side measurement, not the benchmark")
-    ap.add_argument("--path", choices=("encode", "decode", "decode_matvec", "ip"), default="encode",
-                    help="encode = the benchmark; decode / decode_matvec / ip = side measurements of the packed decode kernel, the "
-                         "packed format's consumer kernel and the incoherence-processing kernels")
-    ap.add_argument("--n-out", type=int, default=151936, help="decode_matvec: output rows (default: lm_head of the model shape)")
-    ap.add_argument("--k-in", type=int, default=4096, help="decode_matvec: input columns")
+    ap.add_argument("--path", choices=("encode", "decode", "decode_matvec", "ip", "ldlq"), default="encode",
+                    help="encode = the benchmark; decode / decode_matvec / ip / ldlq = side measurements of the packed decode kernel, the "
+                         "packed format's consumer kernel, the incoherence-processing kernels and the LDLQ matrix of configuration 3")
+    ap.add_argument("--n-out", type=int, default=0, help="side measurements: output rows (defaults: decode_matvec 151936 = lm_head of "
+                                                         "the model shape, ip 12288, ldlq 4096)")
+    ap.add_argument("--k-in", type=int, default=0, help="side measurements: input columns (defaults: decode_matvec 4096, ip 4096, ldlq 12288)")
     ap.add_argument("--m", type=int, default=1, help="decode_matvec: right-hand sides")
     ap.add_argument("--tiles", type=int, default=0,
                     help="encode only the first N tiles of the workload (small cases for ncu captures; the printed line "
@@ -806,7 +877,7 @@ def main() -> None:
         if args.impl != "b200" or args.gpus != 1:
             raise SystemExit(f"--path {args.path} is a one-GPU side measurement of this library")
         if rank == 0:
-            {"decode_matvec": run_decode_matvec, "decode": run_decode, "ip": run_ip}[args.path](args)
+            {"decode_matvec": run_decode_matvec, "decode": run_decode, "ip": run_ip, "ldlq": run_ldlq}[args.path](args)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     elif args.impl == "reference-triton":
