@@ -411,3 +411,18 @@ def test_reference_staging_recipe(tmp_path, monkeypatch):
         fh.write("# edited\n")
     assert make_ref.staged() is None                       # a modified copy is not "the reference"
     shutil.rmtree(tmp_path / "_ref")
+
+
+def test_row_block_wrapper_rejects_bad_arguments_before_touching_the_gpu():
+    """``qtip.encode_rows`` validates shapes, strides and devices on the host; none of these reach the library."""
+    z = torch.zeros(16, 64)
+    with pytest.raises(ValueError, match="16, n_out"):
+        qtip.encode_rows(torch.zeros(8, 64), None, 3, "mcg", torch.zeros(8, 64))
+    with pytest.raises(ValueError, match="n_out % 16"):
+        qtip.encode_rows(torch.zeros(16, 40), None, 3, "mcg", torch.zeros(16, 40))
+    with pytest.raises(ValueError, match="K must be"):
+        qtip.encode_rows(z, None, 5, "mcg", torch.zeros(16, 64))
+    with pytest.raises(ValueError, match="unknown codebook"):
+        qtip.encode_rows(z, None, 3, "nope", torch.zeros(16, 64))
+    with pytest.raises(ValueError, match="CUDA tensors only"):
+        qtip.encode_rows(z, None, 3, "mcg", torch.zeros(16, 64))
